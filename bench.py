@@ -1,0 +1,383 @@
+#!/usr/bin/env python3
+"""Benchmark of the masked flash-attention forward (``mha_fwd_with_mask``) on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload standard] [--impl ours|reference]
+
+One step = one forward pass of the operator over one batch of the workload
+(default "standard": d128 B4 H16 S2048 bf16, 10 % random -inf mask -- the
+configuration the headline metric is quoted on).  Prints ONE JSON line on rank 0.
+
+* ``value``    TFLOPS = 4*B*H*Sq*Sk*d / t (dense convention, mask ignored;
+               reference benchmark/benchmark_fa.py:135-137), kernel launched through
+               the C ABI with every input resident in HBM, summed over ranks.
+* ``e2e``      the same metric through ``ops.mha_fwd_with_mask`` with the inputs in
+               pinned host memory: H2D copies, the operator and the D2H copy of the
+               result are all inside the timed region.
+* ``roofline`` achieved TFLOP/s (or GB/s for the HBM-bound workload) of the
+               attention kernel from CUDA events on the launching stream over the
+               timed region, against the measured peak in MEASURED_PEAKS.json.
+* ``cpu_baseline`` the reference's own C++ CPU attention (oracle/_ref, compiled
+               from its csrc/fa/cpu sources) on the host cores, on a bounded sample.
+
+With ``--gpus N`` (launched under torchrun) every rank runs the workload on its
+own batch shard -- (batch, head) units are independent, there is no collective on
+the data path -- so scaling is weak; the time is the max over ranks.
+
+``--impl reference`` times the reference's CPU implementation of the same
+workload (rank 0 only) and prints the same line shape with "impl": "reference".
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+import torch  # noqa: E402
+
+from custom_ops_b200.workloads import WORKLOADS, make_inputs  # noqa: E402
+
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
+
+# dram__bytes_read.sum + dram__bytes_write.sum of one attention-kernel launch, from
+# the ncu captures summarised under profiles/ (None until a capture exists).
+NCU_TRAFFIC_BYTES = {"standard": None, "splitkv_long": None}
+
+
+def load_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as f:
+            p = json.load(f)
+        return {k: float(p[k]) for k in FALLBACK_PEAKS}, "measured"
+    except Exception:  # noqa: BLE001
+        return dict(FALLBACK_PEAKS), "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi during the timed region."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index = index
+        self.proc = None
+        self.lines = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}",
+                 "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, smax, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in self.lines:
+            parts = [x.strip() for x in line.split(",")]
+            if len(parts) < 7:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                smax.append(float(parts[1]))
+            except ValueError:
+                continue
+            for n, v in zip(names, parts[3:7]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        return {"sm_mhz": statistics.median(sm) if sm else None,
+                "sm_max_mhz": max(smax) if smax else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def dist_env():
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    return rank, world, local
+
+
+# --------------------------------------------------------------------------- reference arm
+def cpu_reference_sample(w, steps: int, warmup: int):
+    """Times the reference's CPU attention on one batch element of workload ``w``
+    (its kernels parallelise over heads only, csrc/fa/cpu/fa_fwd_cpu.cpp:203-204)."""
+    import numpy as np
+    from oracle import oracle
+
+    sample = w.with_batch(1)
+    q, k, v, m = make_inputs(sample, seed=42)
+    from tests.fa_testlib import bits, tag
+    qb, kb, vb, mb = bits(q), bits(k), bits(v), bits(m)
+    dt = tag(q)
+    cores = os.cpu_count() or 1
+    if oracle.load_ref() is not None:
+        kind, isa = "reference", oracle.ref_best_isa()
+        threads = min(sample.H, cores)
+        fn = lambda: oracle.ref_cpu_attn(qb, kb, vb, mb, dt, isa=isa, n_threads=threads)  # noqa: E731
+        what = f"reference csrc/fa/cpu kernel ({isa}), fp32, {threads} threads over heads"
+    elif oracle.load_port() is not None:
+        kind, threads = "port", cores
+        fn = lambda: oracle.port_attn(qb, kb, vb, mb, dt, quantize_p=False, n_threads=threads)  # noqa: E731
+        what = f"C restatement of the reference semantics, fp32, {threads} threads"
+    else:
+        raise RuntimeError("neither oracle/_ref nor the oracle port is built")
+    # The kernels take fp32 buffers; widening the 16-bit inputs is part of the call,
+    # as it is in the reference's own CPU wrapper (csrc/fa/cpu/fa_fwd_cpu.cpp:243-276).
+    for _ in range(warmup):
+        fn()
+    times = []
+    for _ in range(steps):
+        t0 = time.perf_counter()
+        out = fn()
+        times.append(time.perf_counter() - t0)
+    assert np.isfinite(out).all()
+    t = statistics.median(times)
+    return {"value": sample.flops / t / 1e12, "unit": "TFLOPS", "cores": threads, "kind": kind,
+            "sample": f"{what}; one batch element of '{w.name}' (B=1 of {w.B}), "
+                      f"median of {steps} runs, {t * 1e3:.1f} ms each",
+            "host_cores": cores, "ms": t * 1e3}
+
+
+def torch_fp32_cpu_sample(w):
+    """The same masked attention in fp32 torch on the host cores, one batch element."""
+    sample = w.with_batch(1)
+    q, k, v, m = make_inputs(sample, seed=42)
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    g = sample.H // sample.Hk
+
+    def fn():
+        kk = k.float().repeat_interleave(g, dim=1)
+        vv = v.float().repeat_interleave(g, dim=1)
+        s = torch.matmul(q.float(), kk.transpose(-2, -1)) / (sample.d ** 0.5) + m.float()
+        return torch.matmul(torch.softmax(s, dim=-1), vv)
+
+    fn()
+    times = []
+    for _ in range(3):
+        t0 = time.perf_counter()
+        fn()
+        times.append(time.perf_counter() - t0)
+    t = statistics.median(times)
+    return {"value": sample.flops / t / 1e12, "unit": "TFLOPS", "cores": cores,
+            "sample": f"fp32 torch softmax(QK^T*scale+mask)V, one batch element of '{w.name}', "
+                      f"median of 3, {t * 1e3:.1f} ms"}
+
+
+def run_reference_arm(args, w):
+    rank, world, _ = dist_env()
+    if rank != 0:
+        return
+    base = cpu_reference_sample(w, max(1, args.steps), max(1, min(args.warmup, 2)))
+    line = {
+        "impl": "reference", "metric": METRIC, "value": base["value"], "unit": "TFLOPS",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": base["ms"], "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": w.name, "shape": shape_str(w), "sample": "B=1 of the workload"},
+        "cpu_baseline": {k: base[k] for k in ("value", "unit", "cores", "kind", "sample")},
+        "e2e": {"value": base["value"], "unit": "TFLOPS", "h2d_bytes_per_step": 0,
+                "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# --------------------------------------------------------------------------- our arm
+METRIC = "masked attn fwd TFLOPS (d128 B4 H16 S2048, 10% random mask)"
+
+
+def shape_str(w):
+    return (f"d{w.d} B{w.B} H{w.H} Hk{w.Hk} Sq{w.Sq} Sk{w.Sk} "
+            f"{'bf16' if w.dtype == torch.bfloat16 else 'fp16'} mask={w.mask_kind}")
+
+
+def run_ours(args, w):
+    from custom_ops_b200 import _cabi, ops
+
+    rank, world, local = dist_env()
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (the sm_100a kernels have no CPU fallback)")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=dev)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize(dev)
+
+    # every rank owns its own batch shard of the same shape (weak scaling)
+    q_h, k_h, v_h, m_h = make_inputs(w, seed=42 + rank)
+    q_h, k_h, v_h, m_h = (t.pin_memory() for t in (q_h, k_h, v_h, m_h))
+    q, k, v, m = (t.to(dev, non_blocking=True) for t in (q_h, k_h, v_h, m_h))
+    out = torch.empty_like(q)
+    out_h = torch.empty(q.shape, dtype=q.dtype).pin_memory()
+    flush = torch.empty(256 * 1024 * 1024 // 4, dtype=torch.int32, device=dev)
+
+    cargs = _cabi.make_args(
+        q=q.data_ptr(), k=k.data_ptr(), v=v.data_ptr(), mask=m.data_ptr(), out=out.data_ptr(),
+        batch=w.B, heads=w.H, heads_k=w.Hk, seqlen_q=w.Sq, seqlen_k=w.Sk, head_dim=w.d,
+        dtype=_cabi.BF16 if w.dtype == torch.bfloat16 else _cabi.FP16, device=local)
+    plan = _cabi.plan(cargs)
+    ws_bytes = _cabi.workspace_bytes(cargs)
+    ws = torch.empty(max(ws_bytes, 16), dtype=torch.uint8, device=dev)
+    stream = torch.cuda.current_stream(dev)
+    launches_per_step = 1 + (1 if plan.num_splits > 1 else 0) + (1 if plan.mask_repitched else 0)
+
+    def step_kernel():
+        _cabi.forward(cargs, ws.data_ptr(), ws_bytes, stream.cuda_stream)
+
+    def step_e2e():
+        qd = q_h.to(dev, non_blocking=True)
+        kd = k_h.to(dev, non_blocking=True)
+        vd = v_h.to(dev, non_blocking=True)
+        md = m_h.to(dev, non_blocking=True)
+        o = ops.mha_fwd_with_mask(qd, kd, vd, md)
+        out_h.copy_(o, non_blocking=True)
+
+    ops.ensure_loaded("fa")
+    if not ops.is_available("fa"):
+        raise SystemExit(f"operator library failed to load: {ops.load_error('fa')}")
+
+    for _ in range(max(3, args.warmup)):
+        step_kernel()
+    torch.cuda.synchronize(dev)
+
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+
+    # ---- timed region 1: kernel-only, inputs resident in HBM
+    starts = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
+    ends = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
+    barrier()
+    for i in range(args.steps):
+        flush.zero_()                       # evict L2 between steps (outside the events)
+        starts[i].record(stream)
+        step_kernel()
+        ends[i].record(stream)
+    barrier()
+    step_ms = [s.elapsed_time(e) for s, e in zip(starts, ends)]
+    mean_ms = sum(step_ms) / len(step_ms)
+    med_ms = statistics.median(step_ms)
+
+    # ---- timed region 2: end to end from pinned host memory through the operator
+    for _ in range(2):
+        step_e2e()
+    barrier()
+    t0 = time.perf_counter()
+    e0 = torch.cuda.Event(enable_timing=True)
+    e1 = torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    for _ in range(args.steps):
+        step_e2e()
+    e1.record(stream)
+    barrier()
+    e2e_ms = e0.elapsed_time(e1) / args.steps
+    e2e_wall_ms = (time.perf_counter() - t0) * 1e3 / args.steps
+
+    clocks = sampler.stop() if rank == 0 else None
+    status = _cabi.device_status(local, clear=True)
+    if status != 0:
+        raise SystemExit(f"device status word set ({status}): a kernel gave up on a bounded wait")
+
+    if world > 1:
+        t = torch.tensor([mean_ms, med_ms, e2e_ms], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        mean_ms, med_ms, e2e_ms = (float(x) for x in t.tolist())
+
+    if rank == 0:
+        peaks, peak_src = load_peaks()
+        total_flops = w.flops * world
+        value = total_flops / (mean_ms * 1e-3) / 1e12
+        hbm_bound = w.name == "splitkv_long"
+        if hbm_bound:
+            achieved = w.bytes / (mean_ms * 1e-3) / 1e9
+            peak, unit, bound = peaks["hbm_gbs"], "GB/s", "hbm"
+        else:
+            achieved = w.flops / (mean_ms * 1e-3) / 1e12
+            peak, unit, bound = peaks["bf16_tflops"], "TFLOP/s", "tensor"
+        in_bytes = sum(t.numel() * t.element_size() for t in (q_h, k_h, v_h, m_h))
+        line = {
+            "metric": METRIC if w.name == "standard" else f"masked attn fwd TFLOPS ({shape_str(w)})",
+            "value": value, "unit": "TFLOPS", "n_gpus": world, "steps": args.steps,
+            "warmup": max(3, args.warmup), "ms_per_step": mean_ms, "median_ms_per_step": med_ms,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "bf16" if w.dtype == torch.bfloat16 else "fp16", "data": "synthetic",
+            "config": {"workload": w.name, "shape": shape_str(w),
+                       "parallelism": f"(batch, head) sharded, {world} rank(s), no collective",
+                       "global_batch": w.B * world, "l2": "256 MB zero-fill before every timed step",
+                       "timing": "CUDA events per step on the launching stream, mean over steps, max over ranks",
+                       "num_splits": plan.num_splits, "grid": [plan.grid_x, plan.grid_y, plan.grid_z]},
+            "roofline": {"bound": bound, "achieved": achieved, "peak": peak, "unit": unit,
+                         "frac": achieved / peak, "traffic": NCU_TRAFFIC_BYTES.get(w.name),
+                         "peak_source": f"{peak_src} (MEASURED_PEAKS.json burst figure)"
+                         if peak_src == "measured" else "fallback",
+                         "algorithmic_flops": w.flops, "algorithmic_bytes": w.bytes},
+            "e2e": {"value": total_flops / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOPS",
+                    "h2d_bytes_per_step": in_bytes, "d2h_bytes_per_step": out_h.numel() * 2,
+                    "ms_per_step": e2e_ms, "wall_ms_per_step": e2e_wall_ms,
+                    "api": "custom_ops_b200.ops.mha_fwd_with_mask (torch op recsys_ops::mha_fwd_with_mask)"},
+            "gpu_launches": launches_per_step * args.steps,
+            "clocks": clocks,
+        }
+        if world == 1 and not args.no_cpu_baseline:
+            try:
+                base = cpu_reference_sample(w, 3, 1)
+                line["cpu_baseline"] = {k: base[k] for k in ("value", "unit", "cores", "kind", "sample")}
+                line["cpu_torch_fp32"] = torch_fp32_cpu_sample(w)
+            except Exception as e:  # noqa: BLE001
+                line["cpu_baseline"] = {"value": None, "unit": "TFLOPS", "cores": 0, "kind": "port",
+                                        "sample": f"unavailable: {e}"}
+        print(json.dumps(line), flush=True)
+
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawTextHelpFormatter)
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--workload", default="standard", choices=sorted(WORKLOADS))
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    w = WORKLOADS[args.workload]
+    if args.impl == "reference":
+        run_reference_arm(args, w)
+    else:
+        run_ours(args, w)
+
+
+if __name__ == "__main__":
+    main()

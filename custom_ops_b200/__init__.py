@@ -1,0 +1,14 @@
+"""B200-native drop-in for the ``mha_fwd_with_mask`` path of Defyli/custom_ops.
+
+    from custom_ops_b200 import ops
+    out = ops.mha_fwd_with_mask(q, k, v, mask)
+
+mirrors ``from custom_ops import ops`` of the reference (``__init__.py:1222``,
+``recsys.py:641-656``).  Importing the package compiles and loads nothing; the
+native libraries are built (in-tree) and loaded on first use.
+"""
+from .recsys import CustomOps, CustomOpsError, FAOps, RecsysOps  # noqa: F401
+
+ops = RecsysOps()
+
+__all__ = ["ops", "RecsysOps", "FAOps", "CustomOps", "CustomOpsError"]

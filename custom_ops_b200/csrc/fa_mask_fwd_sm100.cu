@@ -1,0 +1,998 @@
+// Masked flash-attention forward for B200 (sm_100a) behind a C ABI.
+//
+//   O = softmax(Q K^T / sqrt(d) + M) V        (M additive: 0, -inf or a finite bias)
+//
+// One CTA owns up to two 128-row query tiles of one (batch, head) and walks a
+// range of 128-key blocks.  Roles inside the CTA:
+//
+//   warps 0-3   softmax group of query tile 0   (thread <-> query row)
+//   warps 4-7   softmax group of query tile 1
+//   warp  8     MMA issuer: one thread issues tcgen05.mma; also owns tensor memory
+//   warp  9     TMA producer: one thread streams Q, K, V tiles into 128B-swizzled
+//               shared memory behind mbarriers
+//
+// Tensor memory (512 columns x 128 lanes of 32 bit):
+//   [  0,128) S of tile 0 (fp32), its first 64 columns are re-used for P (16 bit)
+//   [128,256) S / P of tile 1
+//   [256,256+d) O of tile 0 (fp32)      [384,384+d) O of tile 1
+//
+// Per key block j the MMA thread issues S_t = Q_t K_j^T (operands in shared
+// memory), the softmax group of tile t reads S_t from tensor memory, adds the
+// mask (read straight from global memory, one row segment per thread), keeps a
+// running reference maximum and row sum, writes P_t back to tensor memory in the
+// input dtype, and the MMA thread issues O_t += P_t V_j with P as the
+// tensor-memory operand.  The two tiles alternate, so one tile's softmax runs
+// under the other tile's MMAs.  O is rescaled in tensor memory only when a row's
+// maximum grew by more than 2^8; the final 1/sum normalisation makes that exact.
+//
+// Semantics follow the reference operator (csrc/fa/fa_fwd_op.cu:46-197 and the
+// kernel family it launches, csrc/fa/sm89/fa_fwd_kernel.h:73-480): fp32
+// accumulation, score = s*scale + mask, -inf mask => weight 0, a fully masked row
+// gives 0, columns >= seqlen_k are masked whatever the mask holds, P is rounded
+// to the input dtype before P V, row sums stay fp32.  Split-KV writes normalised
+// fp32 partials plus a natural-log LSE and a second kernel merges them
+// (csrc/fa/sm89/fa_fwd_kernel.h:1406-1545).
+
+#include <cuda.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+#include <cmath>
+#include <cstdint>
+#include <cstring>
+
+#include "../../include/fa_mask_fwd_sm100.h"
+#include "arch_targets.h"
+#include "sm100_ptx.cuh"
+
+namespace fa_sm100 {
+
+constexpr int kBlockM = 128;          // query rows per tile
+constexpr int kBlockN = 128;          // keys per block
+constexpr int kSoftmaxThreads = 128;  // one softmax group
+constexpr int kMmaWarp = 8;
+constexpr int kTmaWarp = 9;
+constexpr int kThreads = 320;
+constexpr uint32_t kTmemCols = 512;
+constexpr float kLog2e = 1.4426950408889634f;
+constexpr float kLn2 = 0.6931471805599453f;
+constexpr float kRescaleThreshold = 8.0f;   // log2 units
+
+// Status codes written to the device status word when a bounded wait runs out.
+enum : uint32_t {
+    kStTmaEmpty = 1, kStMmaQ = 2, kStMmaKv = 3, kStMmaP = 4, kStSoftmaxS = 5, kStSoftmaxO = 6,
+    kStDrain = 7
+};
+
+__device__ unsigned int g_fa_status = 0;
+
+template <int D>
+struct Cfg {
+    static constexpr int kStages = (D == 128) ? 4 : 6;            // K/V ring slots
+    static constexpr uint32_t kTileBytes = kBlockM * D * 2;       // one Q, K or V tile
+    static constexpr uint32_t kSubBytes = 128 * 64 * 2;           // 64-column swizzle panel
+    static constexpr int kSub = D / 64;
+    static constexpr uint32_t kBarBytes = 256;
+    static constexpr uint32_t kSmemBytes = 1024 + 2 * kTileBytes + kStages * kTileBytes + kBarBytes;
+};
+
+struct KParams {
+    const uint16_t* mask;     // rows 16-byte aligned, pitch a multiple of 8 elements
+    void* out;
+    float* lse;
+    float* o_part;            // (splits, B, H, Sq, D) fp32 when num_splits > 1
+    float* lse_part;          // (splits, B, H, Sq)
+    unsigned int* status;
+    long long mask_bs;        // elements
+    long long mask_rs;        // elements
+    int mask_cols;            // readable columns per mask row (multiple of 8, >= Sk)
+    int B, H, Hk, Sq, Sk;
+    int num_splits, blocks_per_split, kv_blocks;
+    int out_fp32;
+    float scale_log2;         // log2(e) / sqrt(d)
+};
+
+template <bool BF16>
+__device__ __forceinline__ void unpack2(uint32_t w, float& lo, float& hi) {
+    if constexpr (BF16) {
+        lo = __uint_as_float(w << 16);
+        hi = __uint_as_float(w & 0xffff0000u);
+    } else {
+        const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w));
+        lo = f.x;
+        hi = f.y;
+    }
+}
+
+template <bool BF16>
+__device__ __forceinline__ uint32_t pack2(float lo, float hi) {
+    if constexpr (BF16) return pack_bf16x2(lo, hi);
+    else return pack_f16x2(lo, hi);
+}
+
+// 32 mask columns (four 16-byte vectors) of one row, zeros where the row or the
+// column is outside the readable mask.
+__device__ __forceinline__ void load_mask32(uint4 (&dst)[4], const uint16_t* row_ptr, int col,
+                                            int mask_cols, bool row_ok) {
+#pragma unroll
+    for (int v = 0; v < 4; ++v) {
+        const int c = col + 8 * v;
+        if (row_ok && c < mask_cols) dst[v] = __ldg(reinterpret_cast<const uint4*>(row_ptr + c));
+        else dst[v] = make_uint4(0u, 0u, 0u, 0u);
+    }
+}
+
+template <int D, bool BF16>
+__global__ void __launch_bounds__(kThreads, 1)
+fa_mask_fwd_kernel(const __grid_constant__ CUtensorMap tm_q,
+                   const __grid_constant__ CUtensorMap tm_k,
+                   const __grid_constant__ CUtensorMap tm_v,
+                   const KParams p) {
+    using C = Cfg<D>;
+    constexpr int NS = C::kStages;
+    constexpr uint32_t TILE = C::kTileBytes;
+    constexpr uint32_t SUB = C::kSubBytes;
+
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t raw_u32 = smem_u32(smem_raw);
+    const uint32_t base = (raw_u32 + 1023u) & ~1023u;
+    const uint32_t sQ = base;
+    const uint32_t sKV = sQ + 2 * TILE;
+    const uint32_t sBar = sKV + NS * TILE;
+    const uint32_t bar_q_full = sBar;              // [2]
+    const uint32_t bar_s_full = sBar + 16;         // [2]
+    const uint32_t bar_p_ready = sBar + 32;        // [2]
+    const uint32_t bar_o_full = sBar + 48;         // [2]
+    const uint32_t bar_kv_full = sBar + 64;        // [NS]
+    const uint32_t bar_kv_empty = sBar + 64 + 8 * NS;  // [NS]
+    uint8_t* bar_generic = smem_raw + (sBar - raw_u32);
+    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(bar_generic + 64 + 16 * NS);
+    volatile uint32_t* abort_flag = tmem_slot + 1;
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+
+    // Once any CTA of any launch gave up on a wait, the status word stays set until
+    // the host clears it; later CTAs leave at once so a broken launch drains quickly.
+    __shared__ uint32_t s_bail;
+    if (threadIdx.x == 0) s_bail = *reinterpret_cast<volatile unsigned int*>(p.status);
+    __syncthreads();
+    if (s_bail != 0) return;
+
+    const int split = blockIdx.x % p.num_splits;
+    const int mpair = blockIdx.x / p.num_splits;
+    const int h = blockIdx.y;
+    const int b = blockIdx.z;
+    const int hk = h / (p.H / p.Hk);
+    const int m0 = mpair * (2 * kBlockM);
+    const bool has_q1 = (m0 + kBlockM) < p.Sq;
+    const int nb_begin = split * p.blocks_per_split;
+    const int nb_end = min(p.kv_blocks, nb_begin + p.blocks_per_split);
+    const int n = nb_end - nb_begin;               // >= 1 by construction of the plan
+
+    if (warp == kTmaWarp && lane == 0) {
+        for (int t = 0; t < 2; ++t) {
+            mbar_init(bar_q_full + 8 * t, 1);
+            mbar_init(bar_s_full + 8 * t, 1);
+            mbar_init(bar_p_ready + 8 * t, kSoftmaxThreads);
+            mbar_init(bar_o_full + 8 * t, 1);
+        }
+        for (int i = 0; i < NS; ++i) {
+            mbar_init(bar_kv_full + 8 * i, 1);
+            mbar_init(bar_kv_empty + 8 * i, 1);
+        }
+        *abort_flag = 0;
+        fence_barrier_init();
+        prefetch_tensormap(&tm_q);
+        prefetch_tensormap(&tm_k);
+        prefetch_tensormap(&tm_v);
+    }
+    if (warp == kMmaWarp) {
+        tmem_alloc(sBar + 64 + 16 * NS, kTmemCols);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == kTmaWarp) {
+        // ------------------------------------------------------------------ TMA producer
+        if (lane == 0) {
+            const int q_plane = b * p.H + h;
+            const int kv_plane = b * p.Hk + hk;
+            mbar_arrive_expect_tx(bar_q_full, TILE);
+#pragma unroll
+            for (int s = 0; s < C::kSub; ++s)
+                tma_load_3d(sQ + s * SUB, &tm_q, bar_q_full, s * 64, m0, q_plane);
+            if (has_q1) {
+                mbar_arrive_expect_tx(bar_q_full + 8, TILE);
+#pragma unroll
+                for (int s = 0; s < C::kSub; ++s)
+                    tma_load_3d(sQ + TILE + s * SUB, &tm_q, bar_q_full + 8, s * 64, m0 + kBlockM,
+                                q_plane);
+            }
+            const int fills = 2 * n;                // K_0, V_0, K_1, V_1, ...
+            int issued = 0;
+            for (int f = 0; f < fills; ++f) {
+                const int slot = f % NS;
+                if (f >= NS &&
+                    !mbar_wait(bar_kv_empty + 8 * slot, ((f / NS) - 1) & 1, abort_flag, p.status,
+                               kStTmaEmpty))
+                    break;
+                const int j = f >> 1;
+                const CUtensorMap* tm = (f & 1) ? &tm_v : &tm_k;
+                const uint32_t dst = sKV + slot * TILE;
+                mbar_arrive_expect_tx(bar_kv_full + 8 * slot, TILE);
+#pragma unroll
+                for (int s = 0; s < C::kSub; ++s)
+                    tma_load_3d(dst + s * SUB, tm, bar_kv_full + 8 * slot, s * 64,
+                                (nb_begin + j) * kBlockN, kv_plane);
+                issued = f + 1;
+            }
+            if (*abort_flag) {
+                // Giving up: let the copies already in flight land before the CTA exits.
+                for (int f = max(0, issued - NS); f < issued; ++f) {
+                    const uint32_t bar = bar_kv_full + 8 * (f % NS);
+                    const uint32_t par = (f / NS) & 1;
+                    bool done = false;
+                    for (uint32_t i = 0; i < kMaxPolls && !done; ++i) done = mbar_try_wait(bar, par);
+                    if (!done) atomicMax(p.status, static_cast<unsigned int>(kStDrain));
+                }
+            }
+        }
+    } else if (warp == kMmaWarp) {
+        // ------------------------------------------------------------------ MMA issuer
+        if (lane == 0) {
+            constexpr uint32_t idesc_s = make_idesc(BF16, false, kBlockM, kBlockN);
+            constexpr uint32_t idesc_o = make_idesc(BF16, true, kBlockM, D);
+            const uint32_t tS0 = tmem_base;
+            const uint32_t tO0 = tmem_base + 256;
+
+            // S_t = Q_t K^T : A and B both K-major, 64-column 128B-swizzled panels.
+            auto issue_s = [&](int t, uint32_t k_addr) {
+#pragma unroll
+                for (int ks = 0; ks < D / 16; ++ks) {
+                    const uint32_t off = (ks >> 2) * SUB + (ks & 3) * 32;
+                    const uint64_t da = smem_desc_sw128(sQ + t * TILE + off, 16, 1024);
+                    const uint64_t db = smem_desc_sw128(k_addr + off, 16, 1024);
+                    mma_ss(tS0 + t * 128, da, db, idesc_s, ks > 0 ? 1u : 0u);
+                }
+            };
+            // O_t += P_t V : A = P in tensor memory (two 16-bit values per column),
+            // B = V tile, d contiguous (MN-major), 16 keys per step.
+            auto issue_pv = [&](int t, uint32_t v_addr, bool acc) {
+#pragma unroll
+                for (int ks = 0; ks < kBlockN / 16; ++ks) {
+                    const uint64_t db = smem_desc_sw128(v_addr + ks * 2048, SUB, 1024);
+                    mma_ts(tO0 + t * 128, tS0 + t * 128 + ks * 8, db, idesc_o,
+                           (acc || ks > 0) ? 1u : 0u);
+                }
+            };
+
+            bool ok = mbar_wait(bar_q_full, 0, abort_flag, p.status, kStMmaQ);
+            ok = ok && mbar_wait(bar_kv_full, 0, abort_flag, p.status, kStMmaKv);
+            if (ok) {
+                tc_fence_after();
+                issue_s(0, sKV);
+                mma_commit(bar_s_full);
+                if (has_q1) {
+                    ok = mbar_wait(bar_q_full + 8, 0, abort_flag, p.status, kStMmaQ);
+                    if (ok) {
+                        tc_fence_after();
+                        issue_s(1, sKV);
+                        mma_commit(bar_s_full + 8);
+                    }
+                }
+                mma_commit(bar_kv_empty);           // K_0's slot
+            }
+            for (int j = 0; ok && j < n; ++j) {
+                const int fv = 2 * j + 1;
+                const int fk = 2 * j + 2;
+                const bool more = (j + 1) < n;
+                const uint32_t v_addr = sKV + (fv % NS) * TILE;
+                const uint32_t k_addr = sKV + (fk % NS) * TILE;
+                if (!(ok = mbar_wait(bar_kv_full + 8 * (fv % NS), (fv / NS) & 1, abort_flag,
+                                     p.status, kStMmaKv)))
+                    break;
+                // ---- tile 0
+                if (!(ok = mbar_wait(bar_p_ready, j & 1, abort_flag, p.status, kStMmaP))) break;
+                tc_fence_after();
+                issue_pv(0, v_addr, j > 0);
+                if (more) {
+                    if (!(ok = mbar_wait(bar_kv_full + 8 * (fk % NS), (fk / NS) & 1, abort_flag,
+                                         p.status, kStMmaKv)))
+                        break;
+                    tc_fence_after();
+                    issue_s(0, k_addr);
+                    mma_commit(bar_s_full);
+                } else {
+                    mma_commit(bar_o_full);
+                }
+                // ---- tile 1
+                if (has_q1) {
+                    if (!(ok = mbar_wait(bar_p_ready + 8, j & 1, abort_flag, p.status, kStMmaP)))
+                        break;
+                    tc_fence_after();
+                    issue_pv(1, v_addr, j > 0);
+                    mma_commit(bar_kv_empty + 8 * (fv % NS));
+                    if (more) {
+                        issue_s(1, k_addr);
+                        mma_commit(bar_s_full + 8);
+                        mma_commit(bar_kv_empty + 8 * (fk % NS));
+                    } else {
+                        mma_commit(bar_o_full + 8);
+                    }
+                } else {
+                    mma_commit(bar_kv_empty + 8 * (fv % NS));
+                    if (more) mma_commit(bar_kv_empty + 8 * (fk % NS));
+                }
+            }
+        }
+    } else if (warp < 4 || has_q1) {
+        // ------------------------------------------------------------------ softmax groups
+        const int t = warp >> 2;
+        const int wq = warp & 3;
+        const int row = m0 + t * kBlockM + wq * 32 + lane;
+        const bool row_ok = row < p.Sq;
+        const uint32_t lane_sel = static_cast<uint32_t>(wq * 32) << 16;
+        const uint32_t tS = tmem_base + lane_sel + t * 128;
+        const uint32_t tO = tmem_base + lane_sel + 256 + t * 128;
+        const uint32_t bar_s = bar_s_full + 8 * t;
+        const uint32_t bar_p = bar_p_ready + 8 * t;
+        const uint16_t* mrow = p.mask + static_cast<long long>(b) * p.mask_bs +
+                               static_cast<long long>(row_ok ? row : 0) * p.mask_rs;
+        const float scale_log2 = p.scale_log2;
+
+        float m_ref = -INFINITY;     // reference maximum, log2 domain
+        float l = 0.f;               // row sum relative to m_ref
+        bool alive = true;
+
+        for (int j = 0; j < n; ++j) {
+            const int col0 = (nb_begin + j) * kBlockN;
+            const bool tail = (col0 + kBlockN) > p.Sk;
+            uint4 mk[2][4];
+            load_mask32(mk[0], mrow, col0, p.mask_cols, row_ok);
+            load_mask32(mk[1], mrow, col0 + 32, p.mask_cols, row_ok);
+
+            bool ok = mbar_wait(bar_s, j & 1, abort_flag, p.status, kStSoftmaxS);
+            if (!__all_sync(0xffffffffu, ok)) { alive = false; break; }
+            tc_fence_after();
+
+            // pass 1: x = s*scale*log2e + mask*log2e, running block maximum
+            float x[kBlockN];
+            float mt = -INFINITY;
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                uint32_t s[32];
+                tmem_ld32(tS + c * 32, s);
+                const uint4(&mc)[4] = mk[c & 1];
+#pragma unroll
+                for (int v = 0; v < 4; ++v) {
+                    const uint32_t w[4] = {mc[v].x, mc[v].y, mc[v].z, mc[v].w};
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) {
+                        float mlo, mhi;
+                        unpack2<BF16>(w[q], mlo, mhi);
+                        const int i = v * 8 + q * 2;
+                        float x0 = fmaf(__uint_as_float(s[i]), scale_log2, mlo * kLog2e);
+                        float x1 = fmaf(__uint_as_float(s[i + 1]), scale_log2, mhi * kLog2e);
+                        if (tail) {
+                            const int cc = col0 + c * 32 + i;
+                            if (cc >= p.Sk) x0 = -INFINITY;
+                            if (cc + 1 >= p.Sk) x1 = -INFINITY;
+                        }
+                        x[c * 32 + i] = x0;
+                        x[c * 32 + i + 1] = x1;
+                        mt = fmaxf(mt, fmaxf(x0, x1));
+                    }
+                }
+                if (c + 2 < 4) load_mask32(mk[c & 1], mrow, col0 + (c + 2) * 32, p.mask_cols, row_ok);
+            }
+
+            // reference maximum moves only when the row maximum grew by more than 2^8
+            const float m_new = fmaxf(m_ref, mt);
+            const bool need = (m_new - m_ref) > kRescaleThreshold;   // NaN (-inf - -inf) -> false
+            float alpha = 1.f;
+            if (need) {
+                alpha = ex2(m_ref - m_new);                          // m_ref = -inf -> 0
+                m_ref = m_new;
+            }
+            if (j > 0 && __any_sync(0xffffffffu, need)) {
+                // PV of the previous block finished before this block's S was committed.
+#pragma unroll
+                for (int c = 0; c < D / 32; ++c) {
+                    uint32_t o[32];
+                    tmem_ld32(tO + c * 32, o);
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+                    tmem_st32(tO + c * 32, o);
+                }
+            }
+
+            // pass 2: p = 2^(x - m_ref), fp32 row sum, P rounded to the input dtype
+            const float m_use = (m_ref == -INFINITY) ? 0.f : m_ref;
+            float sum0 = 0.f, sum1 = 0.f, sum2 = 0.f, sum3 = 0.f;
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                uint32_t pk[16];
+#pragma unroll
+                for (int i = 0; i < 16; i += 2) {
+                    const float p0 = ex2(x[c * 32 + 2 * i] - m_use);
+                    const float p1 = ex2(x[c * 32 + 2 * i + 1] - m_use);
+                    const float p2 = ex2(x[c * 32 + 2 * i + 2] - m_use);
+                    const float p3 = ex2(x[c * 32 + 2 * i + 3] - m_use);
+                    sum0 += p0; sum1 += p1; sum2 += p2; sum3 += p3;
+                    pk[i] = pack2<BF16>(p0, p1);
+                    pk[i + 1] = pack2<BF16>(p2, p3);
+                }
+                tmem_st16(tS + c * 16, pk);
+            }
+            l = l * alpha + ((sum0 + sum1) + (sum2 + sum3));
+            tmem_wait_st();
+            tc_fence_before();
+            mbar_arrive(bar_p);
+        }
+
+        // ---- epilogue: O / l, to the output dtype (or fp32 partial + LSE when split)
+        if (alive) {
+            bool ok = mbar_wait(bar_o_full + 8 * t, 0, abort_flag, p.status, kStSoftmaxO);
+            alive = __all_sync(0xffffffffu, ok);
+        }
+        if (alive) {
+            tc_fence_after();
+            const float inv = (l == 0.f || l != l) ? 1.f : (1.f / l);
+            const float lse_val = (l > 0.f) ? (m_ref + lg2(l)) * kLn2 : -INFINITY;
+            const long long grow = (static_cast<long long>(b) * p.H + h) * p.Sq + row;
+            const bool split_out = p.num_splits > 1;
+            float* o32 = nullptr;
+            if (split_out) {
+                const long long prow =
+                    ((static_cast<long long>(split) * p.B + b) * p.H + h) * p.Sq + row;
+                o32 = p.o_part + prow * D;
+                if (row_ok) p.lse_part[prow] = lse_val;
+            } else {
+                if (p.out_fp32) o32 = static_cast<float*>(p.out) + grow * D;
+                if (row_ok && p.lse != nullptr) p.lse[grow] = lse_val;
+            }
+            uint16_t* o16 = static_cast<uint16_t*>(p.out) + grow * D;
+#pragma unroll
+            for (int c = 0; c < D / 32; ++c) {
+                uint32_t o[32];
+                tmem_ld32(tO + c * 32, o);
+                if (row_ok) {
+                    if (o32 != nullptr) {
+#pragma unroll
+                        for (int i = 0; i < 32; i += 4) {
+                            float4 f;
+                            f.x = __uint_as_float(o[i]) * inv;
+                            f.y = __uint_as_float(o[i + 1]) * inv;
+                            f.z = __uint_as_float(o[i + 2]) * inv;
+                            f.w = __uint_as_float(o[i + 3]) * inv;
+                            *reinterpret_cast<float4*>(o32 + c * 32 + i) = f;
+                        }
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < 32; i += 8) {
+                            uint4 u;
+                            u.x = pack2<BF16>(__uint_as_float(o[i]) * inv, __uint_as_float(o[i + 1]) * inv);
+                            u.y = pack2<BF16>(__uint_as_float(o[i + 2]) * inv, __uint_as_float(o[i + 3]) * inv);
+                            u.z = pack2<BF16>(__uint_as_float(o[i + 4]) * inv, __uint_as_float(o[i + 5]) * inv);
+                            u.w = pack2<BF16>(__uint_as_float(o[i + 6]) * inv, __uint_as_float(o[i + 7]) * inv);
+                            *reinterpret_cast<uint4*>(o16 + c * 32 + i) = u;
+                        }
+                    }
+                }
+            }
+        }
+    }
+
+    __syncwarp();
+    tc_fence_before();
+    __syncthreads();
+    if (warp == kMmaWarp) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, kTmemCols);
+    }
+}
+
+// ---------------------------------------------------------------------------------
+// Split-KV merge: one warp per output row.
+//   out = sum_s w_s o_s / sum_s w_s,  w_s = exp(lse_s - max_s lse_s)
+// ---------------------------------------------------------------------------------
+template <int D>
+__global__ void __launch_bounds__(256)
+fa_mask_combine_kernel(const float* __restrict__ o_parts, const float* __restrict__ lse_parts,
+                       void* __restrict__ out, float* __restrict__ lse_out, int num_parts,
+                       long long rows, int is_bf16, int out_fp32) {
+    constexpr int VEC = D / 32;
+    const int lane = threadIdx.x & 31;
+    const long long row = static_cast<long long>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (row >= rows) return;
+
+    float lse_r[FA_SM100_MAX_SPLITS / 32];
+    float mx = -INFINITY;
+#pragma unroll
+    for (int c = 0; c < FA_SM100_MAX_SPLITS / 32; ++c) {
+        const int s = c * 32 + lane;
+        lse_r[c] = (s < num_parts) ? lse_parts[static_cast<long long>(s) * rows + row] : -INFINITY;
+        mx = fmaxf(mx, lse_r[c]);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    const float mx_use = (mx == -INFINITY) ? 0.f : mx;
+    float w_r[FA_SM100_MAX_SPLITS / 32];
+    float wsum = 0.f;
+#pragma unroll
+    for (int c = 0; c < FA_SM100_MAX_SPLITS / 32; ++c) {
+        w_r[c] = __expf(lse_r[c] - mx_use);            // exp(-inf) = 0 for empty parts
+        wsum += w_r[c];
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) wsum += __shfl_xor_sync(0xffffffffu, wsum, o);
+
+    float acc[VEC];
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) acc[i] = 0.f;
+#pragma unroll
+    for (int c = 0; c < FA_SM100_MAX_SPLITS / 32; ++c) {
+        if (c * 32 >= num_parts) break;
+        const int lim = min(32, num_parts - c * 32);
+        for (int s2 = 0; s2 < lim; ++s2) {
+            const float w = __shfl_sync(0xffffffffu, w_r[c], s2);
+            if (w == 0.f) continue;
+            const float* src = o_parts + (static_cast<long long>(c * 32 + s2) * rows + row) * D + lane * VEC;
+            if constexpr (VEC == 4) {
+                const float4 f = __ldg(reinterpret_cast<const float4*>(src));
+                acc[0] += w * f.x; acc[1] += w * f.y; acc[2] += w * f.z; acc[3] += w * f.w;
+            } else {
+                const float2 f = __ldg(reinterpret_cast<const float2*>(src));
+                acc[0] += w * f.x; acc[1] += w * f.y;
+            }
+        }
+    }
+    const float inv = (wsum > 0.f) ? 1.f / wsum : 0.f;
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) acc[i] *= inv;
+
+    if (out_fp32) {
+        float* dst = static_cast<float*>(out) + row * D + lane * VEC;
+        if constexpr (VEC == 4) *reinterpret_cast<float4*>(dst) = make_float4(acc[0], acc[1], acc[2], acc[3]);
+        else *reinterpret_cast<float2*>(dst) = make_float2(acc[0], acc[1]);
+    } else {
+        uint16_t* dst = static_cast<uint16_t*>(out) + row * D + lane * VEC;
+        if constexpr (VEC == 4) {
+            uint2 u;
+            u.x = is_bf16 ? pack_bf16x2(acc[0], acc[1]) : pack_f16x2(acc[0], acc[1]);
+            u.y = is_bf16 ? pack_bf16x2(acc[2], acc[3]) : pack_f16x2(acc[2], acc[3]);
+            *reinterpret_cast<uint2*>(dst) = u;
+        } else {
+            *reinterpret_cast<uint32_t*>(dst) =
+                is_bf16 ? pack_bf16x2(acc[0], acc[1]) : pack_f16x2(acc[0], acc[1]);
+        }
+    }
+    if (lse_out != nullptr && lane == 0)
+        lse_out[row] = (wsum > 0.f) ? mx + __logf(wsum) : -INFINITY;
+}
+
+// ---------------------------------------------------------------------------------
+// Mask re-pitch: copies the (Sq, Sk) corner of each batch's mask to a pitch that is
+// a multiple of 8 elements so every row starts on a 16-byte boundary.  Pad columns
+// get 0; the attention kernel masks columns >= Sk itself.
+// ---------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256)
+fa_mask_repitch_kernel(const uint16_t* __restrict__ src, uint16_t* __restrict__ dst, int Sq, int Sk,
+                       int pitch, long long src_bs, long long src_rs) {
+    const long long r = blockIdx.x;                  // b * Sq + row
+    const int b = static_cast<int>(r / Sq);
+    const int row = static_cast<int>(r % Sq);
+    const uint16_t* s = src + b * src_bs + row * src_rs;
+    uint16_t* d = dst + r * pitch;
+    for (int c = threadIdx.x; c < pitch; c += blockDim.x) d[c] = (c < Sk) ? s[c] : uint16_t(0);
+}
+
+// ---------------------------------------------------------------------------------
+// Host side
+// ---------------------------------------------------------------------------------
+constexpr int kMaxDevices = 64;
+
+struct DeviceInfo {
+    int sm_count = 0;
+    int cc_major = 0;
+    unsigned int* status_ptr = nullptr;
+    bool attr_set[4] = {false, false, false, false};
+    bool queried = false;
+};
+static DeviceInfo g_dev[kMaxDevices];
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static EncodeTiledFn g_encode = nullptr;
+
+struct DeviceGuard {
+    int prev = -1;
+    bool switched = false;
+    cudaError_t err = cudaSuccess;
+    explicit DeviceGuard(int dev) {
+        err = cudaGetDevice(&prev);
+        if (err == cudaSuccess && prev != dev) {
+            err = cudaSetDevice(dev);
+            switched = (err == cudaSuccess);
+        }
+    }
+    ~DeviceGuard() {
+        if (switched) cudaSetDevice(prev);
+    }
+};
+
+static inline size_t align256(size_t x) { return (x + 255) & ~static_cast<size_t>(255); }
+static inline int ceil_div(int a, int b) { return (a + b - 1) / b; }
+
+static int validate(const FaMaskFwdArgs* a) {
+    if (a == nullptr) return FA_SM100_ERR_NULL;
+    if (a->struct_size != sizeof(FaMaskFwdArgs)) return FA_SM100_ERR_ABI;
+    if (a->dtype != FA_SM100_FP16 && a->dtype != FA_SM100_BF16) return FA_SM100_ERR_DTYPE;
+    if (a->head_dim != 64 && a->head_dim != 128) return FA_SM100_ERR_HEAD_DIM;
+    if (a->batch < 0 || a->heads <= 0 || a->heads_k <= 0 || a->seqlen_q < 0 || a->seqlen_k < 0)
+        return FA_SM100_ERR_SHAPE;
+    if (a->heads % a->heads_k != 0) return FA_SM100_ERR_SHAPE;
+    if (a->heads > 65535 || a->batch > 65535) return FA_SM100_ERR_SHAPE;
+    if (a->mask_seqlen_q < a->seqlen_q || a->mask_seqlen_k < a->seqlen_k) return FA_SM100_ERR_SHAPE;
+    if (a->mask_row_stride < a->mask_seqlen_k || a->mask_batch_stride < 0) return FA_SM100_ERR_SHAPE;
+    if (a->num_splits < 0 || a->num_splits > FA_SM100_MAX_SPLITS) return FA_SM100_ERR_SPLITS;
+    if (a->device < 0 || a->device >= kMaxDevices) return FA_SM100_ERR_SHAPE;
+    return FA_SM100_OK;
+}
+
+// SM count of the device, or the B200 figure where no device can be queried (the
+// planner is also exercised on machines without a GPU).
+static int query_device(int dev, DeviceInfo** out) {
+    DeviceInfo& d = g_dev[dev];
+    if (!d.queried) {
+        int sms = 0, major = 0;
+        if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess &&
+            cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev) == cudaSuccess) {
+            d.sm_count = sms;
+            d.cc_major = major;
+            d.queried = true;
+        } else {
+            cudaGetLastError();
+            d.sm_count = 148;
+            d.cc_major = 0;
+        }
+    }
+    *out = &d;
+    return FA_SM100_OK;
+}
+
+static bool mask_in_place(const FaMaskFwdArgs* a) {
+    const int sk8 = (a->seqlen_k + 7) & ~7;
+    // A NULL mask (planning before the buffers exist) counts as aligned.
+    return (reinterpret_cast<uintptr_t>(a->mask) % 16 == 0) && (a->mask_row_stride % 8 == 0) &&
+           (a->mask_batch_stride % 8 == 0) && (sk8 <= a->mask_row_stride);
+}
+
+static int make_plan(const FaMaskFwdArgs* a, FaMaskFwdPlan* plan) {
+    int rc = validate(a);
+    if (rc != FA_SM100_OK) return rc;
+    DeviceInfo* dev = nullptr;
+    query_device(a->device, &dev);
+    std::memset(plan, 0, sizeof(*plan));
+    const int d = a->head_dim;
+    const int m_pairs = ceil_div(a->seqlen_q, 2 * kBlockM);
+    const int nb = ceil_div(a->seqlen_k, kBlockN);
+    const long long base_ctas = static_cast<long long>(m_pairs) * a->heads * a->batch;
+    int splits = 1;
+    if (nb > 0 && base_ctas > 0) {
+        if (a->num_splits > 0) {
+            splits = a->num_splits;
+        } else if (base_ctas * 5 < static_cast<long long>(dev->sm_count) * 4 && nb >= 8) {
+            // Too few CTAs to fill the GPU: cut the key range so that about one CTA
+            // lands on every SM, keeping at least four key blocks per CTA.
+            const long long by_fill = dev->sm_count / base_ctas;
+            const long long by_work = nb / 4;
+            long long s = by_fill < by_work ? by_fill : by_work;
+            if (s > FA_SM100_MAX_SPLITS) s = FA_SM100_MAX_SPLITS;
+            if (s < 1) s = 1;
+            splits = static_cast<int>(s);
+        }
+        if (splits > nb) splits = nb;
+    }
+    int bps = nb > 0 ? ceil_div(nb, splits) : 0;
+    if (nb > 0) splits = ceil_div(nb, bps);          // no empty split
+    plan->num_splits = splits;
+    plan->kv_blocks = nb;
+    plan->blocks_per_split = bps;
+    plan->q_tiles_per_cta = a->seqlen_q > kBlockM ? 2 : 1;
+    plan->grid_x = m_pairs * splits;
+    plan->grid_y = a->heads;
+    plan->grid_z = a->batch;
+    plan->threads = kThreads;
+    plan->smem_bytes = static_cast<int32_t>(d == 128 ? Cfg<128>::kSmemBytes : Cfg<64>::kSmemBytes);
+    plan->sm_count = dev->sm_count;
+    plan->mask_repitched = (nb > 0 && a->seqlen_q > 0 && !mask_in_place(a)) ? 1 : 0;
+    size_t ws = 0;
+    const size_t rows = static_cast<size_t>(a->batch) * a->heads * a->seqlen_q;
+    if (splits > 1) {
+        ws += align256(static_cast<size_t>(splits) * rows * d * sizeof(float));
+        ws += align256(static_cast<size_t>(splits) * rows * sizeof(float));
+    }
+    if (plan->mask_repitched) {
+        const size_t pitch = (a->seqlen_k + 7) & ~7;
+        ws += align256(static_cast<size_t>(a->batch) * a->seqlen_q * pitch * 2);
+    }
+    plan->workspace_bytes = ws;
+    return FA_SM100_OK;
+}
+
+static int get_encode() {
+    if (g_encode != nullptr) return FA_SM100_OK;
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres) != cudaSuccess ||
+        qres != cudaDriverEntryPointSuccess || fn == nullptr) {
+        cudaGetLastError();
+        return FA_SM100_ERR_CUDA;
+    }
+    g_encode = reinterpret_cast<EncodeTiledFn>(fn);
+    return FA_SM100_OK;
+}
+
+// (planes, rows, d) row-major 16-bit tensor, boxes of 128 rows x 64 columns, 128B swizzle.
+static int encode_map(CUtensorMap* tm, const void* ptr, int dtype, int planes, int rows, int d) {
+    const cuuint64_t dims[3] = {static_cast<cuuint64_t>(d), static_cast<cuuint64_t>(rows),
+                                static_cast<cuuint64_t>(planes)};
+    const cuuint64_t strides[2] = {static_cast<cuuint64_t>(d) * 2,
+                                   static_cast<cuuint64_t>(rows) * d * 2};
+    const cuuint32_t box[3] = {64, 128, 1};
+    const cuuint32_t estr[3] = {1, 1, 1};
+    const CUresult r = g_encode(
+        tm, dtype == FA_SM100_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16,
+        3, const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+        CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? FA_SM100_OK : FA_SM100_ERR_CUDA;
+}
+
+template <int D, bool BF16>
+static int launch_fwd(DeviceInfo* dev, int slot, const CUtensorMap& tq, const CUtensorMap& tk,
+                      const CUtensorMap& tv, const KParams& kp, dim3 grid, cudaStream_t stream) {
+    auto kern = fa_mask_fwd_kernel<D, BF16>;
+    if (!dev->attr_set[slot]) {
+        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 static_cast<int>(Cfg<D>::kSmemBytes)) != cudaSuccess) {
+            cudaGetLastError();
+            return FA_SM100_ERR_CUDA;
+        }
+        dev->attr_set[slot] = true;
+    }
+    kern<<<grid, kThreads, Cfg<D>::kSmemBytes, stream>>>(tq, tk, tv, kp);
+    if (cudaGetLastError() != cudaSuccess) return FA_SM100_ERR_CUDA;
+    return FA_SM100_OK;
+}
+
+static int launch_combine(const float* o_parts, const float* lse_parts, void* out, float* lse_out,
+                          int parts, long long rows, int d, int dtype, int out_fp32,
+                          cudaStream_t stream) {
+    if (rows <= 0) return FA_SM100_OK;
+    const int warps = 8;
+    const unsigned blocks = static_cast<unsigned>((rows + warps - 1) / warps);
+    if (d == 128)
+        fa_mask_combine_kernel<128><<<blocks, warps * 32, 0, stream>>>(
+            o_parts, lse_parts, out, lse_out, parts, rows, dtype == FA_SM100_BF16, out_fp32);
+    else
+        fa_mask_combine_kernel<64><<<blocks, warps * 32, 0, stream>>>(
+            o_parts, lse_parts, out, lse_out, parts, rows, dtype == FA_SM100_BF16, out_fp32);
+    return cudaGetLastError() == cudaSuccess ? FA_SM100_OK : FA_SM100_ERR_CUDA;
+}
+
+static int status_pointer(DeviceInfo* dev) {
+    if (dev->status_ptr == nullptr) {
+        void* ptr = nullptr;
+        if (cudaGetSymbolAddress(&ptr, g_fa_status) != cudaSuccess) {
+            cudaGetLastError();
+            return FA_SM100_ERR_CUDA;
+        }
+        dev->status_ptr = static_cast<unsigned int*>(ptr);
+    }
+    return FA_SM100_OK;
+}
+
+static int forward(const FaMaskFwdArgs* a, void* workspace, size_t workspace_bytes,
+                   cudaStream_t stream) {
+    FaMaskFwdPlan plan;
+    int rc = make_plan(a, &plan);
+    if (rc != FA_SM100_OK) return rc;
+    const long long rows = static_cast<long long>(a->batch) * a->heads * a->seqlen_q;
+    if (rows == 0) return FA_SM100_OK;
+    if (a->q == nullptr || a->out == nullptr) return FA_SM100_ERR_NULL;
+    if (a->seqlen_k > 0 && (a->k == nullptr || a->v == nullptr || a->mask == nullptr))
+        return FA_SM100_ERR_NULL;
+    const uintptr_t align_or = reinterpret_cast<uintptr_t>(a->q) | reinterpret_cast<uintptr_t>(a->k) |
+                               reinterpret_cast<uintptr_t>(a->v) | reinterpret_cast<uintptr_t>(a->out) |
+                               reinterpret_cast<uintptr_t>(workspace);
+    if (align_or % 16 != 0) return FA_SM100_ERR_ALIGN;
+    if (plan.workspace_bytes > 0 && (workspace == nullptr || workspace_bytes < plan.workspace_bytes))
+        return FA_SM100_ERR_WORKSPACE;
+
+    DeviceGuard guard(a->device);
+    if (guard.err != cudaSuccess) {
+        cudaGetLastError();
+        return FA_SM100_ERR_CUDA;
+    }
+    DeviceInfo* dev = nullptr;
+    query_device(a->device, &dev);
+    if (!dev->queried) return FA_SM100_ERR_CUDA;
+    if (dev->cc_major != 10) return FA_SM100_ERR_ARCH;
+
+    const int d = a->head_dim;
+    if (a->seqlen_k == 0) {
+        // No keys: every row is "fully masked" -> 0, LSE -inf.  A merge over zero parts
+        // writes exactly that.
+        return launch_combine(nullptr, nullptr, a->out, a->lse, 0, rows, d, a->dtype, a->out_fp32,
+                              stream);
+    }
+
+    if ((rc = get_encode()) != FA_SM100_OK) return rc;
+    if ((rc = status_pointer(dev)) != FA_SM100_OK) return rc;
+
+    // workspace carve-up: [o_part][lse_part][re-pitched mask]
+    uint8_t* ws = static_cast<uint8_t*>(workspace);
+    float* o_part = nullptr;
+    float* lse_part = nullptr;
+    if (plan.num_splits > 1) {
+        o_part = reinterpret_cast<float*>(ws);
+        ws += align256(static_cast<size_t>(plan.num_splits) * rows * d * sizeof(float));
+        lse_part = reinterpret_cast<float*>(ws);
+        ws += align256(static_cast<size_t>(plan.num_splits) * rows * sizeof(float));
+    }
+    KParams kp;
+    std::memset(&kp, 0, sizeof(kp));
+    if (plan.mask_repitched) {
+        const int pitch = (a->seqlen_k + 7) & ~7;
+        uint16_t* dst = reinterpret_cast<uint16_t*>(ws);
+        const unsigned blocks = static_cast<unsigned>(a->batch) * a->seqlen_q;
+        fa_mask_repitch_kernel<<<blocks, 256, 0, stream>>>(
+            static_cast<const uint16_t*>(a->mask), dst, a->seqlen_q, a->seqlen_k, pitch,
+            a->mask_batch_stride, a->mask_row_stride);
+        if (cudaGetLastError() != cudaSuccess) return FA_SM100_ERR_CUDA;
+        kp.mask = dst;
+        kp.mask_bs = static_cast<long long>(a->seqlen_q) * pitch;
+        kp.mask_rs = pitch;
+        kp.mask_cols = pitch;
+    } else {
+        kp.mask = static_cast<const uint16_t*>(a->mask);
+        kp.mask_bs = a->mask_batch_stride;
+        kp.mask_rs = a->mask_row_stride;
+        kp.mask_cols = (a->seqlen_k + 7) & ~7;
+    }
+    kp.out = a->out;
+    kp.lse = a->lse;
+    kp.o_part = o_part;
+    kp.lse_part = lse_part;
+    kp.status = dev->status_ptr;
+    kp.B = a->batch; kp.H = a->heads; kp.Hk = a->heads_k; kp.Sq = a->seqlen_q; kp.Sk = a->seqlen_k;
+    kp.num_splits = plan.num_splits;
+    kp.blocks_per_split = plan.blocks_per_split;
+    kp.kv_blocks = plan.kv_blocks;
+    kp.out_fp32 = a->out_fp32;
+    kp.scale_log2 = static_cast<float>(1.4426950408889634 / std::sqrt(static_cast<double>(d)));
+
+    CUtensorMap tq, tk, tv;
+    if ((rc = encode_map(&tq, a->q, a->dtype, a->batch * a->heads, a->seqlen_q, d)) != FA_SM100_OK) return rc;
+    if ((rc = encode_map(&tk, a->k, a->dtype, a->batch * a->heads_k, a->seqlen_k, d)) != FA_SM100_OK) return rc;
+    if ((rc = encode_map(&tv, a->v, a->dtype, a->batch * a->heads_k, a->seqlen_k, d)) != FA_SM100_OK) return rc;
+
+    const dim3 grid(plan.grid_x, plan.grid_y, plan.grid_z);
+    const bool bf16 = a->dtype == FA_SM100_BF16;
+    if (d == 128) {
+        rc = bf16 ? launch_fwd<128, true>(dev, 0, tq, tk, tv, kp, grid, stream)
+                  : launch_fwd<128, false>(dev, 1, tq, tk, tv, kp, grid, stream);
+    } else {
+        rc = bf16 ? launch_fwd<64, true>(dev, 2, tq, tk, tv, kp, grid, stream)
+                  : launch_fwd<64, false>(dev, 3, tq, tk, tv, kp, grid, stream);
+    }
+    if (rc != FA_SM100_OK) return rc;
+    if (plan.num_splits > 1)
+        rc = launch_combine(o_part, lse_part, a->out, a->lse, plan.num_splits, rows, d, a->dtype,
+                            a->out_fp32, stream);
+    return rc;
+}
+
+}  // namespace fa_sm100
+
+// ---------------------------------------------------------------------------------
+// C ABI
+// ---------------------------------------------------------------------------------
+extern "C" {
+
+int fa_mask_fwd_sm100_abi_version(void) { return FA_SM100_ABI_VERSION; }
+
+int fa_mask_fwd_sm100_plan(const FaMaskFwdArgs* args, FaMaskFwdPlan* plan) {
+    if (plan == nullptr) return FA_SM100_ERR_NULL;
+    return fa_sm100::make_plan(args, plan);
+}
+
+int fa_mask_fwd_sm100_workspace_bytes(const FaMaskFwdArgs* args, size_t* bytes) {
+    if (bytes == nullptr) return FA_SM100_ERR_NULL;
+    FaMaskFwdPlan plan;
+    const int rc = fa_sm100::make_plan(args, &plan);
+    if (rc != FA_SM100_OK) return rc;
+    *bytes = static_cast<size_t>(plan.workspace_bytes);
+    return FA_SM100_OK;
+}
+
+int fa_mask_fwd_sm100(const FaMaskFwdArgs* args, void* workspace, size_t workspace_bytes,
+                      void* stream) {
+    return fa_sm100::forward(args, workspace, workspace_bytes, static_cast<cudaStream_t>(stream));
+}
+
+int fa_mask_fwd_sm100_combine(const float* o_parts, const float* lse_parts, void* out,
+                              float* lse_out, int32_t num_parts, int64_t rows, int32_t head_dim,
+                              int32_t dtype, int32_t out_fp32, int32_t device, void* stream) {
+    if (out == nullptr || (num_parts > 0 && (o_parts == nullptr || lse_parts == nullptr)))
+        return FA_SM100_ERR_NULL;
+    if (head_dim != 64 && head_dim != 128) return FA_SM100_ERR_HEAD_DIM;
+    if (dtype != FA_SM100_FP16 && dtype != FA_SM100_BF16) return FA_SM100_ERR_DTYPE;
+    if (num_parts < 0 || num_parts > FA_SM100_MAX_SPLITS) return FA_SM100_ERR_SPLITS;
+    if (rows < 0 || device < 0 || device >= fa_sm100::kMaxDevices) return FA_SM100_ERR_SHAPE;
+    fa_sm100::DeviceGuard guard(device);
+    if (guard.err != cudaSuccess) {
+        cudaGetLastError();
+        return FA_SM100_ERR_CUDA;
+    }
+    return fa_sm100::launch_combine(o_parts, lse_parts, out, lse_out, num_parts, rows, head_dim,
+                                    dtype, out_fp32, static_cast<cudaStream_t>(stream));
+}
+
+int fa_mask_fwd_sm100_device_status(int32_t device, uint32_t* status, int32_t clear) {
+    if (status == nullptr) return FA_SM100_ERR_NULL;
+    if (device < 0 || device >= fa_sm100::kMaxDevices) return FA_SM100_ERR_SHAPE;
+    fa_sm100::DeviceGuard guard(device);
+    if (guard.err != cudaSuccess) {
+        cudaGetLastError();
+        return FA_SM100_ERR_CUDA;
+    }
+    unsigned int v = 0;
+    if (cudaDeviceSynchronize() != cudaSuccess) {
+        cudaGetLastError();
+        return FA_SM100_ERR_CUDA;
+    }
+    if (cudaMemcpyFromSymbol(&v, fa_sm100::g_fa_status, sizeof(v)) != cudaSuccess) {
+        cudaGetLastError();
+        return FA_SM100_ERR_CUDA;
+    }
+    *status = v;
+    if (clear && v != 0) {
+        const unsigned int zero = 0;
+        if (cudaMemcpyToSymbol(fa_sm100::g_fa_status, &zero, sizeof(zero)) != cudaSuccess) {
+            cudaGetLastError();
+            return FA_SM100_ERR_CUDA;
+        }
+    }
+    return v == 0 ? FA_SM100_OK : FA_SM100_ERR_DEVICE_WAIT;
+}
+
+const char* fa_mask_fwd_sm100_strerror(int code) {
+    switch (code) {
+        case FA_SM100_OK: return "ok";
+        case FA_SM100_ERR_NULL: return "a required pointer is NULL";
+        case FA_SM100_ERR_DTYPE: return "q must be float16 or bfloat16 (k, v, mask must match)";
+        case FA_SM100_ERR_SHAPE:
+            return "bad shape: sizes must be non-negative, n_heads divisible by n_kv_heads, "
+                   "mask (B, 1, >=Sq, >=Sk)";
+        case FA_SM100_ERR_HEAD_DIM: return "Only head_dim=64 or head_dim=128 is supported";
+        case FA_SM100_ERR_ALIGN: return "q, k, v, out and workspace must be 16-byte aligned";
+        case FA_SM100_ERR_WORKSPACE: return "workspace missing or too small";
+        case FA_SM100_ERR_ARCH: return "no kernel for this GPU: compute capability 10.x (sm_100a) required";
+        case FA_SM100_ERR_CUDA: return "a CUDA call failed";
+        case FA_SM100_ERR_SPLITS: return "num_splits out of range";
+        case FA_SM100_ERR_DEVICE_WAIT: return "a kernel gave up on a bounded wait (device status word set)";
+        case FA_SM100_ERR_ABI: return "FaMaskFwdArgs.struct_size does not match this library";
+        default: return "unknown error";
+    }
+}
+
+}  // extern "C"

@@ -1,0 +1,145 @@
+/*
+ * C ABI of the B200 (sm_100a) masked flash-attention forward.
+ *
+ * This is the boundary a host runtime binds: plain pointers and sizes, no C++
+ * or torch types.  The reference has no C ABI for this path -- its launcher is a
+ * header-only C++ template stack behind a torch operator -- so each entry point
+ * below names the reference interface it stands in for.
+ *
+ * Conventions: every function returns FA_SM100_OK (0) or a negative
+ * FA_SM100_ERR_* code, never throws, never synchronises the device (except
+ * fa_mask_fwd_sm100_device_status, which says so) and never allocates device
+ * memory: outputs and the workspace belong to the caller.  Work is enqueued on
+ * the caller's stream.
+ */
+#ifndef FA_MASK_FWD_SM100_H_
+#define FA_MASK_FWD_SM100_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define FA_SM100_ABI_VERSION 1
+
+enum {
+    FA_SM100_OK = 0,
+    FA_SM100_ERR_NULL = -1,        /* a required pointer is NULL */
+    FA_SM100_ERR_DTYPE = -2,       /* dtype is neither FA_SM100_FP16 nor FA_SM100_BF16 */
+    FA_SM100_ERR_SHAPE = -3,       /* negative size, Hk does not divide H, mask smaller than (Sq,Sk) */
+    FA_SM100_ERR_HEAD_DIM = -4,    /* head_dim is neither 64 nor 128 */
+    FA_SM100_ERR_ALIGN = -5,       /* q/k/v/out/workspace not 16-byte aligned */
+    FA_SM100_ERR_WORKSPACE = -6,   /* workspace missing or smaller than workspace_bytes() says */
+    FA_SM100_ERR_ARCH = -7,        /* the device is not compute capability 10.x */
+    FA_SM100_ERR_CUDA = -8,        /* a CUDA runtime / driver call failed */
+    FA_SM100_ERR_SPLITS = -9,      /* num_splits outside [0, FA_SM100_MAX_SPLITS] */
+    FA_SM100_ERR_DEVICE_WAIT = -10,/* a kernel gave up on a bounded wait (see device_status) */
+    FA_SM100_ERR_ABI = -11         /* struct_size does not match this library */
+};
+
+enum { FA_SM100_FP16 = 0, FA_SM100_BF16 = 1 };
+
+#define FA_SM100_MAX_SPLITS 128
+
+/*
+ * Arguments of one forward call.  Field meanings follow the reference's
+ * FA_mask_params (csrc/fa/common/fa_fwd_params.h:18-71) as filled by
+ * mha_fwd_with_mask_cuda (csrc/fa/fa_fwd_op.cu:144-188): contiguous tensors
+ *   q    (batch, heads,   seqlen_q, head_dim)
+ *   k, v (batch, heads_k, seqlen_k, head_dim)
+ *   mask (batch, 1, mask_seqlen_q >= seqlen_q, mask_seqlen_k >= seqlen_k)
+ *   out  (batch, heads,   seqlen_q, head_dim)
+ * all of the same 16-bit dtype.  The mask is additive (0 visible, -inf masked,
+ * finite = bias), has no head dimension, and is addressed through its element
+ * strides; columns >= seqlen_k are always masked whatever the mask holds there
+ * and rows >= seqlen_q are never read.  The softmax scale is fixed at
+ * 1/sqrt(head_dim).  Unlike the reference, seqlen_k and the mask pitch need no
+ * multiple-of-8 padding by the caller (the reference pads K, V and the mask with
+ * three copies, csrc/fa/fa_fwd_op.cu:117-138): K and V are read in place and only
+ * a mask whose pitch or base breaks 16-byte row alignment is re-pitched into the
+ * workspace.
+ */
+typedef struct FaMaskFwdArgs {
+    uint32_t struct_size;       /* sizeof(FaMaskFwdArgs), checked */
+    int32_t device;             /* CUDA device ordinal the pointers live on */
+    const void* q;
+    const void* k;
+    const void* v;
+    const void* mask;
+    void* out;                  /* input dtype unless out_fp32 != 0 */
+    float* lse;                 /* optional (batch, heads, seqlen_q) natural-log LSE, or NULL */
+    int32_t batch;
+    int32_t heads;
+    int32_t heads_k;
+    int32_t seqlen_q;
+    int32_t seqlen_k;
+    int32_t head_dim;
+    int32_t mask_seqlen_q;
+    int32_t mask_seqlen_k;
+    int64_t mask_batch_stride;  /* elements */
+    int64_t mask_row_stride;    /* elements */
+    int32_t dtype;              /* FA_SM100_FP16 / FA_SM100_BF16 */
+    int32_t num_splits;         /* 0 = choose, 1 = never split, n = force n KV splits */
+    int32_t out_fp32;           /* 1: `out` is fp32 (normalised partial for a cross-GPU merge) */
+    int32_t reserved;
+} FaMaskFwdArgs;
+
+/* What the launcher decided for a set of arguments; for tests and tuning. */
+typedef struct FaMaskFwdPlan {
+    int32_t num_splits;         /* KV splits actually used (1 = single pass) */
+    int32_t kv_blocks;          /* number of 128-key blocks */
+    int32_t blocks_per_split;
+    int32_t q_tiles_per_cta;    /* 128-row query tiles handled by one CTA */
+    int32_t grid_x, grid_y, grid_z;
+    int32_t threads;
+    int32_t smem_bytes;
+    int32_t mask_repitched;     /* 1 when the mask is first copied to an aligned pitch */
+    int32_t sm_count;
+    int32_t reserved;
+    uint64_t workspace_bytes;
+} FaMaskFwdPlan;
+
+/* Library / ABI version (FA_SM100_ABI_VERSION of the build). */
+int fa_mask_fwd_sm100_abi_version(void);
+
+/* Validates `args` and reports the launch plan without touching the device's
+ * memory.  Replaces the policy half of fa_fwd_launch / fa_launch_sm8x
+ * (csrc/fa/fa_fwd_launch.h:137-170, 262-309): split count, grid, workspace. */
+int fa_mask_fwd_sm100_plan(const FaMaskFwdArgs* args, FaMaskFwdPlan* plan);
+
+/* Bytes of scratch the call needs (0 is possible).  Replaces the per-call
+ * torch::empty of the split-KV partial buffers (csrc/fa/fa_fwd_launch.h:289-297). */
+int fa_mask_fwd_sm100_workspace_bytes(const FaMaskFwdArgs* args, size_t* bytes);
+
+/* Enqueues the forward on `stream` (a cudaStream_t passed as void*).  Replaces
+ * mha_fwd_with_mask_cuda's launch half and fa_fwd_launch
+ * (csrc/fa/fa_fwd_op.cu:141-197, csrc/fa/fa_fwd_launch.h:573-603). */
+int fa_mask_fwd_sm100(const FaMaskFwdArgs* args, void* workspace, size_t workspace_bytes,
+                      void* stream);
+
+/* Merges `num_parts` normalised fp32 partial results that cover disjoint key
+ * ranges: out = sum_s exp(lse_s - max) * o_s / sum_s exp(lse_s - max), rows whose
+ * every lse is -inf give 0.  `o_parts` is (num_parts, rows, head_dim) fp32,
+ * `lse_parts` (num_parts, rows) fp32, `out` (rows, head_dim) of `dtype`, or fp32
+ * when out_fp32 != 0; `lse_out` (rows) is optional.  Same maths as the reference
+ * combine kernel (csrc/fa/sm89/fa_fwd_kernel.h:1406-1545); exported so a
+ * cross-GPU Split-KV can merge gathered partials. */
+int fa_mask_fwd_sm100_combine(const float* o_parts, const float* lse_parts, void* out,
+                              float* lse_out, int32_t num_parts, int64_t rows, int32_t head_dim,
+                              int32_t dtype, int32_t out_fp32, int32_t device, void* stream);
+
+/* Synchronises `device` and returns in *status the sticky device-side status
+ * word: 0, or the code of the first bounded wait that ran out.  Clears it when
+ * `clear` != 0.  No counterpart in the reference, whose kernels wait unbounded. */
+int fa_mask_fwd_sm100_device_status(int32_t device, uint32_t* status, int32_t clear);
+
+/* Text for a return code.  Stands in for the TORCH_CHECK messages of
+ * csrc/fa/fa_fwd_op.cu:53-108 and csrc/fa/fa_fwd_launch.h:596-602. */
+const char* fa_mask_fwd_sm100_strerror(int code);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FA_MASK_FWD_SM100_H_ */

@@ -1,0 +1,284 @@
+"""GPU parity tests of mha_fwd_with_mask: the sm_100a kernels, called through the
+C ABI and through the torch operator, against the CPU oracle on the same seeded
+inputs.  The matrix mirrors the reference's own test script
+(tests/test_mha_fwd_with_mask.py:181-230) and its cross-arch suite
+(tests/remote_verify_suite.py:109-161).
+
+Tolerances (floating point, written here as the bar demands):
+  * vs the fp32 oracle softmax(QK^T*scale+mask)V: max-abs <= 2e-2, mean-abs <= 2e-3
+  * vs the reference test oracle (P rounded to the input dtype):
+    max_err < 1e-2 or max_err/max|ref| < 1e-2
+"""
+import numpy as np
+import pytest
+import torch
+
+from custom_ops_b200 import _cabi
+from custom_ops_b200.workloads import WORKLOADS, make_inputs, small_analogue
+from oracle import oracle
+from tests.fa_testlib import (bits, check_against_oracle, from_bits, make_case, run_cabi, tag)
+
+pytestmark = pytest.mark.gpu
+
+DTYPES = [torch.bfloat16, torch.float16]
+
+
+def _cuda(*ts):
+    return [t.cuda() for t in ts]
+
+
+@pytest.fixture(autouse=True)
+def _clean_device_status():
+    yield
+    st = _cabi.device_status(0, clear=True)
+    assert st == 0, f"a kernel gave up on a bounded wait, status code {st}"
+
+
+# ---------------------------------------------------------------- golden fixtures
+def test_golden_fixtures_through_cabi(golden):
+    """Committed inputs + outputs of the reference's ref_attn."""
+    for name in (str(n) for n in golden["names"]):
+        dt = str(golden[f"{name}.dtype"])
+        q, k, v, m = (from_bits(golden[f"{name}.{x}"], dt).cuda() for x in ("q", "k", "v", "mask"))
+        out, _, _ = run_cabi(q, k, v, m)
+        ref = oracle.to_f32(golden[f"{name}.out"], dt)
+        o = out.float().cpu().numpy()
+        assert np.all(np.isfinite(o)), name
+        mx = np.abs(o - ref).max()
+        assert mx < 1e-2 or mx / (np.abs(ref).max() + 1e-8) < 1e-2, (name, mx)
+
+
+# ---------------------------------------------------------------- base path
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("shape", [(2, 16, 256, 256, 64), (2, 16, 256, 256, 128),
+                                   (1, 24, 512, 384, 64), (1, 24, 384, 512, 128)])
+def test_base_zero_mask(dtype, shape):
+    b, h, sq, sk, d = shape
+    q, k, v, m = _cuda(*make_case(b, h, h, sq, sk, d, dtype, "zero", seed=1))
+    out, _, plan = run_cabi(q, k, v, m)
+    check_against_oracle(out, q, k, v, m, f"base{shape}")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("d", [64, 128])
+@pytest.mark.parametrize("kind", ["causal", "random", "block", "all_masked_row", "drop10",
+                                  "drop_bias"])
+def test_mask_semantics(dtype, d, kind):
+    q, k, v, m = _cuda(*make_case(2, 4, 4, 256, 256, d, dtype, kind, seed=2))
+    out, _, _ = run_cabi(q, k, v, m)
+    check_against_oracle(out, q, k, v, m, f"{kind}_d{d}")
+    if kind == "all_masked_row":
+        assert torch.all(out[:, :, 0, :] == 0)
+
+
+# ---------------------------------------------------------------- ragged shapes
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("case", [
+    (1, 8, 100, 104, 64, "zero"), (1, 8, 100, 200, 128, "random"),
+    (1, 8, 256, 1032, 128, "random"), (1, 8, 64, 56, 64, "random"),
+    (1, 8, 128, 8, 128, "causal"), (1, 4, 1, 104, 64, "random"),
+    (1, 1, 64, 100, 64, "drop10"),
+])
+def test_unaligned_shapes(dtype, case):
+    b, h, sq, sk, d, kind = case
+    q, k, v, m = _cuda(*make_case(b, h, h, sq, sk, d, dtype, kind, seed=3))
+    out, _, _ = run_cabi(q, k, v, m)
+    check_against_oracle(out, q, k, v, m, f"unaligned{case}")
+
+
+@pytest.mark.parametrize("sk", [1, 7, 9, 55, 63, 100, 101, 777, 1031, 2053])
+def test_ragged_sk_sweep(sk):
+    """Sk % 8 != 0: K and V are read in place, only the mask is re-pitched."""
+    q, k, v, m = _cuda(*make_case(1, 2, 2, 65, sk, 128, torch.bfloat16, "drop_bias", seed=sk))
+    out, _, plan = run_cabi(q, k, v, m)
+    assert plan.mask_repitched == (1 if sk % 8 else 0)
+    check_against_oracle(out, q, k, v, m, f"sk{sk}")
+
+
+@pytest.mark.parametrize("sq", [1, 3, 63, 65, 127, 129, 333, 1000])
+def test_ragged_sq_sweep(sq):
+    q, k, v, m = _cuda(*make_case(1, 2, 2, sq, 264, 64, torch.float16, "drop_bias", seed=sq))
+    out, _, _ = run_cabi(q, k, v, m)
+    check_against_oracle(out, q, k, v, m, f"sq{sq}")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("pad", [(0, 8), (8, 8), (13, 5), (0, 3)])
+def test_prepadded_mask_trap_values(dtype, pad):
+    """Mask larger than (Sq, Sk) with visible-looking values in the pad: columns
+    >= Sk are always masked, rows >= Sq never read."""
+    pr, pc = pad
+    q, k, v, m = _cuda(*make_case(1, 8, 8, 100, 104, 64, dtype, "random", seed=4,
+                                  pad_rows=pr, pad_cols=pc))
+    out, _, _ = run_cabi(q, k, v, m)
+    crop = m[:, :, :100, :104].contiguous()
+    check_against_oracle(out, q, k, v, crop, f"prepad{pad}")
+
+
+# ---------------------------------------------------------------- GQA
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("case", [(2, 16, 4, 256, 256, 64), (1, 32, 8, 512, 384, 128),
+                                  (1, 2, 1, 130, 200, 128), (1, 12, 3, 77, 136, 64)])
+def test_gqa(dtype, case):
+    b, h, hk, sq, sk, d = case
+    q, k, v, m = _cuda(*make_case(b, h, hk, sq, sk, d, dtype, "drop_bias", seed=5))
+    out, _, _ = run_cabi(q, k, v, m)
+    check_against_oracle(out, q, k, v, m, f"gqa{case}")
+
+
+# ---------------------------------------------------------------- split-KV
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("case", [
+    (1, 1, 128, 8192, 64, "zero"), (1, 1, 64, 4096, 64, "causal"),
+    (1, 2, 128, 8192, 128, "zero"), (1, 2, 256, 16384, 128, "random"),
+    (1, 2, 128, 1032, 128, "random"),
+])
+def test_splitkv_auto(dtype, case):
+    b, h, sq, sk, d, kind = case
+    q, k, v, m = _cuda(*make_case(b, h, h, sq, sk, d, dtype, kind, seed=6))
+    out, _, plan = run_cabi(q, k, v, m)
+    if sk >= 4096:
+        assert plan.num_splits > 1
+    check_against_oracle(out, q, k, v, m, f"splitkv{case}")
+
+
+@pytest.mark.parametrize("splits", [2, 3, 7, 40, 128])
+def test_splitkv_forced_counts(splits):
+    """Non-power-of-two counts, uneven ranges, more splits asked than key blocks."""
+    q, k, v, m = _cuda(*make_case(1, 3, 3, 130, 1300, 128, torch.bfloat16, "drop_bias", seed=7))
+    out, lse, plan = run_cabi(q, k, v, m, num_splits=splits, want_lse=True)
+    assert 1 <= plan.num_splits <= min(splits, plan.kv_blocks)
+    check_against_oracle(out, q, k, v, m, f"forced{splits}")
+    ref_lse = oracle.lse_fp32(bits(q), bits(k), bits(m), "bf16")
+    assert np.abs(lse.cpu().numpy() - ref_lse).max() < 2e-3
+
+
+def test_splitkv_fully_masked_row_and_whole_splits_masked():
+    """A row masked everywhere stays 0 through the merge; splits whose every key is
+    masked contribute nothing (lse = -inf)."""
+    q, k, v, m = make_case(1, 2, 1, 128, 4096, 128, torch.bfloat16, "zero", seed=8)
+    m[:, :, 5, :] = float("-inf")
+    m[:, :, :, 1024:] = float("-inf")          # only the first quarter is visible
+    q, k, v, m = _cuda(q, k, v, m)
+    out, lse, plan = run_cabi(q, k, v, m, num_splits=40, want_lse=True)
+    assert plan.num_splits > 8
+    check_against_oracle(out, q, k, v, m, "split_masked")
+    assert torch.all(out[:, :, 5, :] == 0)
+    assert torch.all(torch.isneginf(lse[:, :, 5]))
+
+
+def test_fp32_partial_output_and_merge_entry_point():
+    """out_fp32 + lse of two key halves, merged by fa_mask_fwd_sm100_combine, equal
+    the single-pass result: the building block of the cross-GPU Split-KV."""
+    q, k, v, m = _cuda(*make_case(1, 4, 4, 128, 2048, 128, torch.bfloat16, "drop_bias", seed=9))
+    full, _, _ = run_cabi(q, k, v, m)
+    parts, lses = [], []
+    for lo, hi in ((0, 1024), (1024, 2048)):
+        o, l, _ = run_cabi(q, k[:, :, lo:hi].contiguous(), v[:, :, lo:hi].contiguous(),
+                           m[:, :, :, lo:hi].contiguous(), want_lse=True, out_fp32=True)
+        parts.append(o)
+        lses.append(l)
+    o_parts = torch.stack(parts).contiguous()
+    lse_parts = torch.stack(lses).contiguous()
+    merged = torch.empty_like(full)
+    rows = 4 * 128
+    _cabi.combine(o_parts.data_ptr(), lse_parts.data_ptr(), merged.data_ptr(), 0, 2, rows, 128,
+                  _cabi.BF16, 0, 0, torch.cuda.current_stream().cuda_stream)
+    torch.cuda.synchronize()
+    assert (merged.float() - full.float()).abs().max() < 4e-3
+    check_against_oracle(merged, q, k, v, m, "merged halves")
+
+
+# ---------------------------------------------------------------- the five configurations
+@pytest.mark.parametrize("name,sq,sk,bh", [
+    ("plumbing", 256, 256, (2, 4)), ("standard", 384, 640, (1, 4)),
+    ("gqa_window", 768, 768, (1, 8)), ("splitkv_long", 128, 8192, (1, 4)),
+    ("ragged_items", 200, 1027, (1, 8)),
+])
+def test_config_small_analogues(name, sq, sk, bh):
+    w = small_analogue(WORKLOADS[name], sq, sk, B=bh[0], H=bh[1])
+    q, k, v, m = _cuda(*make_inputs(w, seed=42))
+    out, _, _ = run_cabi(q, k, v, m)
+    check_against_oracle(out, q, k, v, m, name)
+
+
+@pytest.mark.parametrize("name", ["plumbing", "standard", "gqa_window", "splitkv_long",
+                                  "ragged_items"])
+def test_config_full_size(name):
+    """Full BASELINE sizes.  The C oracle is run on a subset of (batch, head) pairs
+    to keep this in seconds; a size-independent property covers the rest: with a
+    mask that hides everything but one key per row, the output row equals that
+    key's V row exactly (rounded), for every (b, h, row)."""
+    w = WORKLOADS[name]
+    q, k, v, m = make_inputs(w, seed=42)
+    qc, kc, vc, mc = _cuda(q, k, v, m)
+    out, _, _ = run_cabi(qc, kc, vc, mc)
+    assert torch.isfinite(out.float()).all()
+    g = w.H // w.Hk
+    for (b, hk) in [(0, 0), (w.B - 1, w.Hk - 1)]:
+        hs = slice(hk * g, hk * g + min(g, 2))
+        check_against_oracle(out[b:b + 1, hs], q[b:b + 1, hs], k[b:b + 1, hk:hk + 1].expand(
+            1, hs.stop - hs.start, w.Sk, w.d).contiguous(), v[b:b + 1, hk:hk + 1].expand(
+            1, hs.stop - hs.start, w.Sk, w.d).contiguous(), m[b:b + 1], f"{name}[{b},{hk}]")
+    # one-hot property over the whole tensor
+    gen = torch.Generator().manual_seed(7)
+    pick = torch.randint(0, w.Sk, (w.B, w.Sq), generator=gen)
+    onehot = torch.full((w.B, 1, w.Sq, w.Sk), float("-inf"), dtype=w.dtype)
+    onehot.scatter_(3, pick.view(w.B, 1, w.Sq, 1), 0.0)
+    out1, _, _ = run_cabi(qc, kc, vc, onehot.cuda())
+    idx = pick.cuda().view(w.B, 1, w.Sq, 1).expand(w.B, w.Hk, w.Sq, w.d)
+    want = torch.gather(vc, 2, idx).repeat_interleave(g, dim=1)
+    assert torch.equal(out1, want)
+
+
+# ---------------------------------------------------------------- torch operator boundary
+def test_torch_operator_matches_cabi_and_errors():
+    from custom_ops_b200 import ops
+    q, k, v, m = _cuda(*make_case(2, 4, 2, 130, 300, 128, torch.bfloat16, "drop_bias", seed=11))
+    out = ops.mha_fwd_with_mask(q, k, v, m)
+    assert ops.is_available("fa"), ops.load_error("fa")
+    ref, _, _ = run_cabi(q, k, v, m)
+    assert out.dtype == q.dtype and out.shape == q.shape
+    assert torch.equal(out, ref)
+    assert torch.equal(torch.ops.recsys_ops.mha_fwd_with_mask(q, k, v, m), ref)
+    # Sk % 8 != 0 is handled, not rejected (tests/test_mha_fwd_with_mask.py:133-149)
+    q2, k2, v2, m2 = _cuda(*make_case(1, 1, 1, 64, 100, 64, torch.float16, "zero", seed=12))
+    m2[..., ::7] = float("-inf")
+    check_against_oracle(ops.mha_fwd_with_mask(q2, k2, v2, m2), q2, k2, v2, m2, "autopad")
+    # fp32 input and mixed dtypes raise RuntimeError (tests/test_mha_fwd_with_mask.py:150-169)
+    x = torch.randn(1, 1, 64, 64, device="cuda")
+    with pytest.raises(RuntimeError):
+        ops.mha_fwd_with_mask(x, x, x, torch.zeros(1, 1, 64, 64, device="cuda"))
+    qh = x.half()
+    with pytest.raises(RuntimeError):
+        ops.mha_fwd_with_mask(qh, x.bfloat16(), qh, torch.zeros(1, 1, 64, 64, device="cuda").half())
+    with pytest.raises(RuntimeError):
+        ops.mha_fwd_with_mask(qh.transpose(2, 3), qh, qh, torch.zeros(1, 1, 64, 64, device="cuda").half())
+
+
+def test_torch_compile_uses_fake_impl():
+    from custom_ops_b200 import ops
+    ops.ensure_loaded("fa")
+    q, k, v, m = _cuda(*make_case(1, 2, 2, 128, 128, 64, torch.bfloat16, "causal", seed=13))
+
+    def f(q, k, v, m):
+        return torch.ops.recsys_ops.mha_fwd_with_mask(q, k, v, m) * 2
+
+    eager = f(q, k, v, m)
+    compiled = torch.compile(f, backend="aot_eager", fullgraph=True)(q, k, v, m)
+    assert torch.equal(eager, compiled)
+
+
+def test_cabi_rejects_bad_arguments_on_device():
+    q, k, v, m = _cuda(*make_case(1, 1, 1, 64, 64, 64, torch.bfloat16, "zero", seed=14))
+    out = torch.empty_like(q)
+    good = dict(q=q.data_ptr(), k=k.data_ptr(), v=v.data_ptr(), mask=m.data_ptr(),
+                out=out.data_ptr(), batch=1, heads=1, heads_k=1, seqlen_q=64, seqlen_k=64,
+                head_dim=64, dtype=_cabi.BF16)
+    with pytest.raises(_cabi.FaSm100Error) as e:
+        _cabi.forward(_cabi.make_args(**{**good, "q": q.data_ptr() + 2}), 0, 0, 0)
+    assert e.value.code == -5
+    with pytest.raises(_cabi.FaSm100Error) as e:
+        a = _cabi.make_args(**{**good, "seqlen_k": 4096, "mask_seqlen_k": 4096, "num_splits": 4})
+        _cabi.forward(a, 0, 0, 0)
+    assert e.value.code == -6
