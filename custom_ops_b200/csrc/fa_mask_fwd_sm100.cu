@@ -3,13 +3,20 @@
 //   O = softmax(Q K^T / sqrt(d) + M) V        (M additive: 0, -inf or a finite bias)
 //
 // One CTA owns up to two 128-row query tiles of one (batch, head) and walks a
-// range of 128-key blocks.  Roles inside the CTA:
+// range of 128-key blocks.  Roles inside the CTA (12 warps):
 //
 //   warps 0-3   softmax group of query tile 0   (thread <-> query row)
 //   warps 4-7   softmax group of query tile 1
 //   warp  8     MMA issuer: one thread issues tcgen05.mma; also owns tensor memory
-//   warp  9     TMA producer: one thread streams Q, K, V tiles into 128B-swizzled
-//               shared memory behind mbarriers
+//   warp  9     TMA producer for Q, K, V tiles
+//   warp 10     TMA producer for the mask tiles
+//   warp 11     idle (completes the warpgroup for the register re-balancing)
+//
+// Everything the tensor cores and the softmax threads touch arrives through TMA
+// into 128-byte-swizzled shared memory behind mbarrier rings: Q (resident), a
+// ring of K/V tiles, and per query tile two 128x64 mask panels.  The softmax
+// threads read their own mask row from the swizzled panel with 16-byte loads,
+// which the swizzle makes bank-conflict free.
 //
 // Tensor memory (512 columns x 128 lanes of 32 bit):
 //   [  0,128) S of tile 0 (fp32), its first 64 columns are re-used for P (16 bit)
@@ -18,10 +25,9 @@
 //
 // Per key block j the MMA thread issues S_t = Q_t K_j^T (operands in shared
 // memory), the softmax group of tile t reads S_t from tensor memory, adds the
-// mask (read straight from global memory, one row segment per thread), keeps a
-// running reference maximum and row sum, writes P_t back to tensor memory in the
-// input dtype, and the MMA thread issues O_t += P_t V_j with P as the
-// tensor-memory operand.  The two tiles alternate, so one tile's softmax runs
+// mask, keeps a running reference maximum and row sum, writes P_t back to tensor
+// memory in the input dtype, and the MMA thread issues O_t += P_t V_j with P as
+// the tensor-memory operand.  The two tiles alternate, so one tile's softmax runs
 // under the other tile's MMAs.  O is rescaled in tensor memory only when a row's
 // maximum grew by more than 2^8; the final 1/sum normalisation makes that exact.
 //
@@ -52,55 +58,51 @@ constexpr int kBlockN = 128;          // keys per block
 constexpr int kSoftmaxThreads = 128;  // one softmax group
 constexpr int kMmaWarp = 8;
 constexpr int kTmaWarp = 9;
-constexpr int kThreads = 320;
+constexpr int kMaskWarp = 10;
+constexpr int kThreads = 384;
 constexpr uint32_t kTmemCols = 512;
 constexpr float kLog2e = 1.4426950408889634f;
-constexpr float kLn2 = 0.6931471805599453f;
-constexpr float kRescaleThreshold = 8.0f;   // log2 units
+constexpr float kRescaleThreshold = 5.545177444479562f;   // 8 * ln 2: rescale when max grew > 2^8
+constexpr uint32_t kPanelBytes = 128 * 64 * 2;            // 128 rows x 64 columns, 16 bit
 
 // Status codes written to the device status word when a bounded wait runs out.
 enum : uint32_t {
     kStTmaEmpty = 1, kStMmaQ = 2, kStMmaKv = 3, kStMmaP = 4, kStSoftmaxS = 5, kStSoftmaxO = 6,
-    kStDrain = 7
+    kStDrain = 7, kStMaskEmpty = 8, kStSoftmaxMask = 9
 };
 
 __device__ unsigned int g_fa_status = 0;
 
 template <int D>
 struct Cfg {
-    static constexpr int kStages = (D == 128) ? 4 : 6;            // K/V ring slots
+    static constexpr int kStages = (D == 128) ? 3 : 6;            // K/V ring slots
     static constexpr uint32_t kTileBytes = kBlockM * D * 2;       // one Q, K or V tile
-    static constexpr uint32_t kSubBytes = 128 * 64 * 2;           // 64-column swizzle panel
+    static constexpr uint32_t kSubBytes = kPanelBytes;            // 64-column swizzle panel
     static constexpr int kSub = D / 64;
+    static constexpr uint32_t kMaskBytes = 4 * kPanelBytes;       // 2 tiles x 2 panels
     static constexpr uint32_t kBarBytes = 256;
-    static constexpr uint32_t kSmemBytes = 1024 + 2 * kTileBytes + kStages * kTileBytes + kBarBytes;
+    static constexpr uint32_t kSmemBytes =
+        1024 + 2 * kTileBytes + kStages * kTileBytes + kMaskBytes + kBarBytes;
 };
 
 struct KParams {
-    const uint16_t* mask;     // rows 16-byte aligned, pitch a multiple of 8 elements
     void* out;
     float* lse;
     float* o_part;            // (splits, B, H, Sq, D) fp32 when num_splits > 1
     float* lse_part;          // (splits, B, H, Sq)
     unsigned int* status;
-    long long mask_bs;        // elements
-    long long mask_rs;        // elements
-    int mask_cols;            // readable columns per mask row (multiple of 8, >= Sk)
     int B, H, Hk, Sq, Sk;
     int num_splits, blocks_per_split, kv_blocks;
     int out_fp32;
-    float scale_log2;         // log2(e) / sqrt(d)
+    float scale;              // 1 / sqrt(d)
 };
 
 template <bool BF16>
-__device__ __forceinline__ void unpack2(uint32_t w, float& lo, float& hi) {
+__device__ __forceinline__ float2 unpack2(uint32_t w) {
     if constexpr (BF16) {
-        lo = __uint_as_float(w << 16);
-        hi = __uint_as_float(w & 0xffff0000u);
+        return make_float2(__uint_as_float(w << 16), __uint_as_float(w & 0xffff0000u));
     } else {
-        const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w));
-        lo = f.x;
-        hi = f.y;
+        return __half22float2(*reinterpret_cast<const __half2*>(&w));
     }
 }
 
@@ -110,23 +112,12 @@ __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
     else return pack_f16x2(lo, hi);
 }
 
-// 32 mask columns (four 16-byte vectors) of one row, zeros where the row or the
-// column is outside the readable mask.
-__device__ __forceinline__ void load_mask32(uint4 (&dst)[4], const uint16_t* row_ptr, int col,
-                                            int mask_cols, bool row_ok) {
-#pragma unroll
-    for (int v = 0; v < 4; ++v) {
-        const int c = col + 8 * v;
-        if (row_ok && c < mask_cols) dst[v] = __ldg(reinterpret_cast<const uint4*>(row_ptr + c));
-        else dst[v] = make_uint4(0u, 0u, 0u, 0u);
-    }
-}
-
 template <int D, bool BF16>
 __global__ void __launch_bounds__(kThreads, 1)
 fa_mask_fwd_kernel(const __grid_constant__ CUtensorMap tm_q,
                    const __grid_constant__ CUtensorMap tm_k,
                    const __grid_constant__ CUtensorMap tm_v,
+                   const __grid_constant__ CUtensorMap tm_m,
                    const KParams p) {
     using C = Cfg<D>;
     constexpr int NS = C::kStages;
@@ -138,15 +129,19 @@ fa_mask_fwd_kernel(const __grid_constant__ CUtensorMap tm_q,
     const uint32_t base = (raw_u32 + 1023u) & ~1023u;
     const uint32_t sQ = base;
     const uint32_t sKV = sQ + 2 * TILE;
-    const uint32_t sBar = sKV + NS * TILE;
-    const uint32_t bar_q_full = sBar;              // [2]
-    const uint32_t bar_s_full = sBar + 16;         // [2]
-    const uint32_t bar_p_ready = sBar + 32;        // [2]
-    const uint32_t bar_o_full = sBar + 48;         // [2]
-    const uint32_t bar_kv_full = sBar + 64;        // [NS]
-    const uint32_t bar_kv_empty = sBar + 64 + 8 * NS;  // [NS]
+    const uint32_t sM = sKV + NS * TILE;               // [tile][panel] of kPanelBytes
+    const uint32_t sBar = sM + C::kMaskBytes;
+    const uint32_t bar_q_full = sBar;                  // [2]
+    const uint32_t bar_s_full = sBar + 16;             // [2]
+    const uint32_t bar_p_ready = sBar + 32;            // [2]
+    const uint32_t bar_o_full = sBar + 48;             // [2]
+    const uint32_t bar_m_full = sBar + 64;             // [4]
+    const uint32_t bar_m_empty = sBar + 96;            // [4]
+    const uint32_t bar_kv_full = sBar + 128;           // [NS]
+    const uint32_t bar_kv_empty = sBar + 128 + 8 * NS; // [NS]
+    const uint32_t tmem_slot_addr = sBar + 128 + 16 * NS;
     uint8_t* bar_generic = smem_raw + (sBar - raw_u32);
-    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(bar_generic + 64 + 16 * NS);
+    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(bar_generic + 128 + 16 * NS);
     volatile uint32_t* abort_flag = tmem_slot + 1;
 
     const int warp = threadIdx.x >> 5;
@@ -177,6 +172,10 @@ fa_mask_fwd_kernel(const __grid_constant__ CUtensorMap tm_q,
             mbar_init(bar_p_ready + 8 * t, kSoftmaxThreads);
             mbar_init(bar_o_full + 8 * t, 1);
         }
+        for (int i = 0; i < 4; ++i) {
+            mbar_init(bar_m_full + 8 * i, 1);
+            mbar_init(bar_m_empty + 8 * i, kSoftmaxThreads);
+        }
         for (int i = 0; i < NS; ++i) {
             mbar_init(bar_kv_full + 8 * i, 1);
             mbar_init(bar_kv_empty + 8 * i, 1);
@@ -186,9 +185,10 @@ fa_mask_fwd_kernel(const __grid_constant__ CUtensorMap tm_q,
         prefetch_tensormap(&tm_q);
         prefetch_tensormap(&tm_k);
         prefetch_tensormap(&tm_v);
+        prefetch_tensormap(&tm_m);
     }
     if (warp == kMmaWarp) {
-        tmem_alloc(sBar + 64 + 16 * NS, kTmemCols);
+        tmem_alloc(tmem_slot_addr, kTmemCols);
         tmem_relinquish();
     }
     tc_fence_before();
@@ -196,290 +196,334 @@ fa_mask_fwd_kernel(const __grid_constant__ CUtensorMap tm_q,
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
 
-    if (warp == kTmaWarp) {
-        // ------------------------------------------------------------------ TMA producer
-        if (lane == 0) {
-            const int q_plane = b * p.H + h;
-            const int kv_plane = b * p.Hk + hk;
-            mbar_arrive_expect_tx(bar_q_full, TILE);
-#pragma unroll
-            for (int s = 0; s < C::kSub; ++s)
-                tma_load_3d(sQ + s * SUB, &tm_q, bar_q_full, s * 64, m0, q_plane);
-            if (has_q1) {
-                mbar_arrive_expect_tx(bar_q_full + 8, TILE);
+    if (warp >= 8) {
+        // Data-movement and MMA-issue warps need few registers; hand the rest to softmax.
+        reg_dealloc<56>();
+        if (warp == kTmaWarp) {
+            // -------------------------------------------------------------- Q/K/V producer
+            if (lane == 0) {
+                const int q_plane = b * p.H + h;
+                const int kv_plane = b * p.Hk + hk;
+                mbar_arrive_expect_tx(bar_q_full, TILE);
 #pragma unroll
                 for (int s = 0; s < C::kSub; ++s)
-                    tma_load_3d(sQ + TILE + s * SUB, &tm_q, bar_q_full + 8, s * 64, m0 + kBlockM,
-                                q_plane);
-            }
-            const int fills = 2 * n;                // K_0, V_0, K_1, V_1, ...
-            int issued = 0;
-            for (int f = 0; f < fills; ++f) {
-                const int slot = f % NS;
-                if (f >= NS &&
-                    !mbar_wait(bar_kv_empty + 8 * slot, ((f / NS) - 1) & 1, abort_flag, p.status,
-                               kStTmaEmpty))
-                    break;
-                const int j = f >> 1;
-                const CUtensorMap* tm = (f & 1) ? &tm_v : &tm_k;
-                const uint32_t dst = sKV + slot * TILE;
-                mbar_arrive_expect_tx(bar_kv_full + 8 * slot, TILE);
-#pragma unroll
-                for (int s = 0; s < C::kSub; ++s)
-                    tma_load_3d(dst + s * SUB, tm, bar_kv_full + 8 * slot, s * 64,
-                                (nb_begin + j) * kBlockN, kv_plane);
-                issued = f + 1;
-            }
-            if (*abort_flag) {
-                // Giving up: let the copies already in flight land before the CTA exits.
-                for (int f = max(0, issued - NS); f < issued; ++f) {
-                    const uint32_t bar = bar_kv_full + 8 * (f % NS);
-                    const uint32_t par = (f / NS) & 1;
-                    bool done = false;
-                    for (uint32_t i = 0; i < kMaxPolls && !done; ++i) done = mbar_try_wait(bar, par);
-                    if (!done) atomicMax(p.status, static_cast<unsigned int>(kStDrain));
-                }
-            }
-        }
-    } else if (warp == kMmaWarp) {
-        // ------------------------------------------------------------------ MMA issuer
-        if (lane == 0) {
-            constexpr uint32_t idesc_s = make_idesc(BF16, false, kBlockM, kBlockN);
-            constexpr uint32_t idesc_o = make_idesc(BF16, true, kBlockM, D);
-            const uint32_t tS0 = tmem_base;
-            const uint32_t tO0 = tmem_base + 256;
-
-            // S_t = Q_t K^T : A and B both K-major, 64-column 128B-swizzled panels.
-            auto issue_s = [&](int t, uint32_t k_addr) {
-#pragma unroll
-                for (int ks = 0; ks < D / 16; ++ks) {
-                    const uint32_t off = (ks >> 2) * SUB + (ks & 3) * 32;
-                    const uint64_t da = smem_desc_sw128(sQ + t * TILE + off, 16, 1024);
-                    const uint64_t db = smem_desc_sw128(k_addr + off, 16, 1024);
-                    mma_ss(tS0 + t * 128, da, db, idesc_s, ks > 0 ? 1u : 0u);
-                }
-            };
-            // O_t += P_t V : A = P in tensor memory (two 16-bit values per column),
-            // B = V tile, d contiguous (MN-major), 16 keys per step.
-            auto issue_pv = [&](int t, uint32_t v_addr, bool acc) {
-#pragma unroll
-                for (int ks = 0; ks < kBlockN / 16; ++ks) {
-                    const uint64_t db = smem_desc_sw128(v_addr + ks * 2048, SUB, 1024);
-                    mma_ts(tO0 + t * 128, tS0 + t * 128 + ks * 8, db, idesc_o,
-                           (acc || ks > 0) ? 1u : 0u);
-                }
-            };
-
-            bool ok = mbar_wait(bar_q_full, 0, abort_flag, p.status, kStMmaQ);
-            ok = ok && mbar_wait(bar_kv_full, 0, abort_flag, p.status, kStMmaKv);
-            if (ok) {
-                tc_fence_after();
-                issue_s(0, sKV);
-                mma_commit(bar_s_full);
+                    tma_load_3d(sQ + s * SUB, &tm_q, bar_q_full, s * 64, m0, q_plane);
                 if (has_q1) {
-                    ok = mbar_wait(bar_q_full + 8, 0, abort_flag, p.status, kStMmaQ);
-                    if (ok) {
-                        tc_fence_after();
-                        issue_s(1, sKV);
-                        mma_commit(bar_s_full + 8);
+                    mbar_arrive_expect_tx(bar_q_full + 8, TILE);
+#pragma unroll
+                    for (int s = 0; s < C::kSub; ++s)
+                        tma_load_3d(sQ + TILE + s * SUB, &tm_q, bar_q_full + 8, s * 64,
+                                    m0 + kBlockM, q_plane);
+                }
+                const int fills = 2 * n;                // K_0, V_0, K_1, V_1, ...
+                int issued = 0;
+                for (int f = 0; f < fills; ++f) {
+                    const int slot = f % NS;
+                    if (f >= NS &&
+                        !mbar_wait(bar_kv_empty + 8 * slot, ((f / NS) - 1) & 1, abort_flag,
+                                   p.status, kStTmaEmpty))
+                        break;
+                    const int j = f >> 1;
+                    const CUtensorMap* tm = (f & 1) ? &tm_v : &tm_k;
+                    const uint32_t dst = sKV + slot * TILE;
+                    mbar_arrive_expect_tx(bar_kv_full + 8 * slot, TILE);
+#pragma unroll
+                    for (int s = 0; s < C::kSub; ++s)
+                        tma_load_3d(dst + s * SUB, tm, bar_kv_full + 8 * slot, s * 64,
+                                    (nb_begin + j) * kBlockN, kv_plane);
+                    issued = f + 1;
+                }
+                if (*abort_flag) {
+                    // Giving up: let the copies already in flight land before the CTA exits.
+                    for (int f = max(0, issued - NS); f < issued; ++f) {
+                        const uint32_t bar = bar_kv_full + 8 * (f % NS);
+                        const uint32_t par = (f / NS) & 1;
+                        bool done = false;
+                        for (uint32_t i = 0; i < kMaxPolls && !done; ++i) done = mbar_try_wait(bar, par);
+                        if (!done) atomicMax(p.status, static_cast<unsigned int>(kStDrain));
                     }
                 }
-                mma_commit(bar_kv_empty);           // K_0's slot
             }
-            for (int j = 0; ok && j < n; ++j) {
-                const int fv = 2 * j + 1;
-                const int fk = 2 * j + 2;
-                const bool more = (j + 1) < n;
-                const uint32_t v_addr = sKV + (fv % NS) * TILE;
-                const uint32_t k_addr = sKV + (fk % NS) * TILE;
-                if (!(ok = mbar_wait(bar_kv_full + 8 * (fv % NS), (fv / NS) & 1, abort_flag,
-                                     p.status, kStMmaKv)))
-                    break;
-                // ---- tile 0
-                if (!(ok = mbar_wait(bar_p_ready, j & 1, abort_flag, p.status, kStMmaP))) break;
-                tc_fence_after();
-                issue_pv(0, v_addr, j > 0);
-                if (more) {
-                    if (!(ok = mbar_wait(bar_kv_full + 8 * (fk % NS), (fk / NS) & 1, abort_flag,
+        } else if (warp == kMaskWarp) {
+            // -------------------------------------------------------------- mask producer
+            if (lane == 0) {
+                const int tiles = has_q1 ? 2 : 1;
+                int last_j = -1;
+                bool ok = true;
+                for (int j = 0; ok && j < n; ++j) {
+                    const int col0 = (nb_begin + j) * kBlockN;
+                    for (int i = 0; ok && i < 2 * tiles; ++i) {     // i = tile * 2 + panel
+                        if (j > 0 && !mbar_wait(bar_m_empty + 8 * i, (j - 1) & 1, abort_flag,
+                                                p.status, kStMaskEmpty)) {
+                            ok = false;
+                            break;
+                        }
+                        mbar_arrive_expect_tx(bar_m_full + 8 * i, kPanelBytes);
+                        tma_load_3d(sM + i * kPanelBytes, &tm_m, bar_m_full + 8 * i,
+                                    col0 + (i & 1) * 64, m0 + (i >> 1) * kBlockM, b);
+                    }
+                    if (ok) last_j = j;
+                }
+                if (*abort_flag && last_j >= 0) {
+                    for (int i = 0; i < 2 * tiles; ++i) {
+                        bool done = false;
+                        for (uint32_t it = 0; it < kMaxPolls && !done; ++it)
+                            done = mbar_try_wait(bar_m_full + 8 * i, last_j & 1);
+                        if (!done) atomicMax(p.status, static_cast<unsigned int>(kStDrain));
+                    }
+                }
+            }
+        } else if (warp == kMmaWarp) {
+            // -------------------------------------------------------------- MMA issuer
+            if (lane == 0) {
+                constexpr uint32_t idesc_s = make_idesc(BF16, false, kBlockM, kBlockN);
+                constexpr uint32_t idesc_o = make_idesc(BF16, true, kBlockM, D);
+                const uint32_t tS0 = tmem_base;
+                const uint32_t tO0 = tmem_base + 256;
+
+                // S_t = Q_t K^T : A and B both K-major, 64-column 128B-swizzled panels.
+                auto issue_s = [&](int t, uint32_t k_addr) {
+#pragma unroll
+                    for (int ks = 0; ks < D / 16; ++ks) {
+                        const uint32_t off = (ks >> 2) * SUB + (ks & 3) * 32;
+                        const uint64_t da = smem_desc_sw128(sQ + t * TILE + off, 16, 1024);
+                        const uint64_t db = smem_desc_sw128(k_addr + off, 16, 1024);
+                        mma_ss(tS0 + t * 128, da, db, idesc_s, ks > 0 ? 1u : 0u);
+                    }
+                };
+                // O_t += P_t V : A = P in tensor memory (two 16-bit values per column),
+                // B = V tile, d contiguous (MN-major), 16 keys per step.
+                auto issue_pv = [&](int t, uint32_t v_addr, bool acc) {
+#pragma unroll
+                    for (int ks = 0; ks < kBlockN / 16; ++ks) {
+                        const uint64_t db = smem_desc_sw128(v_addr + ks * 2048, SUB, 1024);
+                        mma_ts(tO0 + t * 128, tS0 + t * 128 + ks * 8, db, idesc_o,
+                               (acc || ks > 0) ? 1u : 0u);
+                    }
+                };
+
+                bool ok = mbar_wait(bar_q_full, 0, abort_flag, p.status, kStMmaQ);
+                ok = ok && mbar_wait(bar_kv_full, 0, abort_flag, p.status, kStMmaKv);
+                if (ok) {
+                    tc_fence_after();
+                    issue_s(0, sKV);
+                    mma_commit(bar_s_full);
+                    if (has_q1) {
+                        ok = mbar_wait(bar_q_full + 8, 0, abort_flag, p.status, kStMmaQ);
+                        if (ok) {
+                            tc_fence_after();
+                            issue_s(1, sKV);
+                            mma_commit(bar_s_full + 8);
+                        }
+                    }
+                    mma_commit(bar_kv_empty);           // K_0's slot
+                }
+                for (int j = 0; ok && j < n; ++j) {
+                    const int fv = 2 * j + 1;
+                    const int fk = 2 * j + 2;
+                    const bool more = (j + 1) < n;
+                    const uint32_t v_addr = sKV + (fv % NS) * TILE;
+                    const uint32_t k_addr = sKV + (fk % NS) * TILE;
+                    if (!(ok = mbar_wait(bar_kv_full + 8 * (fv % NS), (fv / NS) & 1, abort_flag,
                                          p.status, kStMmaKv)))
                         break;
+                    // ---- tile 0
+                    if (!(ok = mbar_wait(bar_p_ready, j & 1, abort_flag, p.status, kStMmaP))) break;
                     tc_fence_after();
-                    issue_s(0, k_addr);
-                    mma_commit(bar_s_full);
-                } else {
-                    mma_commit(bar_o_full);
-                }
-                // ---- tile 1
-                if (has_q1) {
-                    if (!(ok = mbar_wait(bar_p_ready + 8, j & 1, abort_flag, p.status, kStMmaP)))
-                        break;
-                    tc_fence_after();
-                    issue_pv(1, v_addr, j > 0);
-                    mma_commit(bar_kv_empty + 8 * (fv % NS));
+                    issue_pv(0, v_addr, j > 0);
                     if (more) {
-                        issue_s(1, k_addr);
-                        mma_commit(bar_s_full + 8);
-                        mma_commit(bar_kv_empty + 8 * (fk % NS));
+                        if (!(ok = mbar_wait(bar_kv_full + 8 * (fk % NS), (fk / NS) & 1, abort_flag,
+                                             p.status, kStMmaKv)))
+                            break;
+                        tc_fence_after();
+                        issue_s(0, k_addr);
+                        mma_commit(bar_s_full);
                     } else {
-                        mma_commit(bar_o_full + 8);
+                        mma_commit(bar_o_full);
                     }
-                } else {
-                    mma_commit(bar_kv_empty + 8 * (fv % NS));
-                    if (more) mma_commit(bar_kv_empty + 8 * (fk % NS));
+                    // ---- tile 1
+                    if (has_q1) {
+                        if (!(ok = mbar_wait(bar_p_ready + 8, j & 1, abort_flag, p.status, kStMmaP)))
+                            break;
+                        tc_fence_after();
+                        issue_pv(1, v_addr, j > 0);
+                        mma_commit(bar_kv_empty + 8 * (fv % NS));
+                        if (more) {
+                            issue_s(1, k_addr);
+                            mma_commit(bar_s_full + 8);
+                            mma_commit(bar_kv_empty + 8 * (fk % NS));
+                        } else {
+                            mma_commit(bar_o_full + 8);
+                        }
+                    } else {
+                        mma_commit(bar_kv_empty + 8 * (fv % NS));
+                        if (more) mma_commit(bar_kv_empty + 8 * (fk % NS));
+                    }
                 }
             }
         }
-    } else if (warp < 4 || has_q1) {
-        // ------------------------------------------------------------------ softmax groups
-        const int t = warp >> 2;
-        const int wq = warp & 3;
-        const int row = m0 + t * kBlockM + wq * 32 + lane;
-        const bool row_ok = row < p.Sq;
-        const uint32_t lane_sel = static_cast<uint32_t>(wq * 32) << 16;
-        const uint32_t tS = tmem_base + lane_sel + t * 128;
-        const uint32_t tO = tmem_base + lane_sel + 256 + t * 128;
-        const uint32_t bar_s = bar_s_full + 8 * t;
-        const uint32_t bar_p = bar_p_ready + 8 * t;
-        const uint16_t* mrow = p.mask + static_cast<long long>(b) * p.mask_bs +
-                               static_cast<long long>(row_ok ? row : 0) * p.mask_rs;
-        const float scale_log2 = p.scale_log2;
+    } else {
+        reg_alloc<224>();
+        if (warp < 4 || has_q1) {
+            // -------------------------------------------------------------- softmax groups
+            const int t = warp >> 2;
+            const int wq = warp & 3;
+            const int row_in_tile = wq * 32 + lane;
+            const int row = m0 + t * kBlockM + row_in_tile;
+            const bool row_ok = row < p.Sq;
+            const uint32_t lane_sel = static_cast<uint32_t>(wq * 32) << 16;
+            const uint32_t tS = tmem_base + lane_sel + t * 128;
+            const uint32_t tO = tmem_base + lane_sel + 256 + t * 128;
+            const uint32_t bar_s = bar_s_full + 8 * t;
+            const uint32_t bar_p = bar_p_ready + 8 * t;
+            // this thread's row inside a swizzled mask panel: 16-byte chunk c of row r
+            // lives at r*128 + ((c ^ (r & 7)) << 4)
+            const uint32_t m_row_addr = sM + (2 * t) * kPanelBytes + row_in_tile * 128;
+            const uint32_t m_xor = static_cast<uint32_t>(row_in_tile & 7) << 4;
+            const float2 scale2 = make_float2(p.scale, p.scale);
 
-        float m_ref = -INFINITY;     // reference maximum, log2 domain
-        float l = 0.f;               // row sum relative to m_ref
-        bool alive = true;
+            float m_ref = -INFINITY;     // reference maximum of the scaled, masked scores
+            float l = 0.f;               // row sum relative to m_ref
+            bool alive = true;
 
-        for (int j = 0; j < n; ++j) {
-            const int col0 = (nb_begin + j) * kBlockN;
-            const bool tail = (col0 + kBlockN) > p.Sk;
-            uint4 mk[2][4];
-            load_mask32(mk[0], mrow, col0, p.mask_cols, row_ok);
-            load_mask32(mk[1], mrow, col0 + 32, p.mask_cols, row_ok);
+            for (int j = 0; j < n; ++j) {
+                const int col0 = (nb_begin + j) * kBlockN;
+                const bool tail = (col0 + kBlockN) > p.Sk;
 
-            bool ok = mbar_wait(bar_s, j & 1, abort_flag, p.status, kStSoftmaxS);
-            if (!__all_sync(0xffffffffu, ok)) { alive = false; break; }
-            tc_fence_after();
+                bool ok = mbar_wait(bar_s, j & 1, abort_flag, p.status, kStSoftmaxS);
+                if (!__all_sync(0xffffffffu, ok)) { alive = false; break; }
+                tc_fence_after();
 
-            // pass 1: x = s*scale*log2e + mask*log2e, running block maximum
-            float x[kBlockN];
-            float mt = -INFINITY;
+                // pass 1: x = s*scale + mask, block maximum
+                float2 x[kBlockN / 2];
+                float mt0 = -INFINITY, mt1 = -INFINITY;
 #pragma unroll
-            for (int c = 0; c < 4; ++c) {
-                uint32_t s[32];
-                tmem_ld32(tS + c * 32, s);
-                const uint4(&mc)[4] = mk[c & 1];
+                for (int pn = 0; pn < 2; ++pn) {
+                    ok = mbar_wait(bar_m_full + 8 * (2 * t + pn), j & 1, abort_flag, p.status,
+                                   kStSoftmaxMask);
+                    if (!__all_sync(0xffffffffu, ok)) { alive = false; break; }
+                    uint32_t s[64];
+                    tmem_ld64(tS + pn * 64, s);
 #pragma unroll
-                for (int v = 0; v < 4; ++v) {
-                    const uint32_t w[4] = {mc[v].x, mc[v].y, mc[v].z, mc[v].w};
+                    for (int c = 0; c < 8; ++c) {
+                        const uint4 mv = lds128(m_row_addr + pn * kPanelBytes +
+                                                ((static_cast<uint32_t>(c) << 4) ^ m_xor));
+                        const uint32_t w[4] = {mv.x, mv.y, mv.z, mv.w};
 #pragma unroll
-                    for (int q = 0; q < 4; ++q) {
-                        float mlo, mhi;
-                        unpack2<BF16>(w[q], mlo, mhi);
-                        const int i = v * 8 + q * 2;
-                        float x0 = fmaf(__uint_as_float(s[i]), scale_log2, mlo * kLog2e);
-                        float x1 = fmaf(__uint_as_float(s[i + 1]), scale_log2, mhi * kLog2e);
-                        if (tail) {
-                            const int cc = col0 + c * 32 + i;
-                            if (cc >= p.Sk) x0 = -INFINITY;
-                            if (cc + 1 >= p.Sk) x1 = -INFINITY;
+                        for (int q = 0; q < 4; ++q) {
+                            const int i = c * 8 + q * 2;                  // column inside the panel
+                            const float2 mk = unpack2<BF16>(w[q]);
+                            const float2 sv = make_float2(__uint_as_float(s[i]), __uint_as_float(s[i + 1]));
+                            float2 xv = __ffma2_rn(sv, scale2, mk);
+                            if (tail) {
+                                const int cc = col0 + pn * 64 + i;
+                                if (cc >= p.Sk) xv.x = -INFINITY;
+                                if (cc + 1 >= p.Sk) xv.y = -INFINITY;
+                            }
+                            x[pn * 32 + c * 4 + q] = xv;
+                            mt0 = fmaxf(mt0, xv.x);
+                            mt1 = fmaxf(mt1, xv.y);
                         }
-                        x[c * 32 + i] = x0;
-                        x[c * 32 + i + 1] = x1;
-                        mt = fmaxf(mt, fmaxf(x0, x1));
+                    }
+                    mbar_arrive(bar_m_empty + 8 * (2 * t + pn));      // panel may be refilled
+                }
+                if (!alive) break;
+                const float mt = fmaxf(mt0, mt1);
+
+                // reference maximum moves only when the row maximum grew by more than 2^8
+                const float m_new = fmaxf(m_ref, mt);
+                const bool need = (m_new - m_ref) > kRescaleThreshold;  // NaN (-inf - -inf) -> false
+                float alpha = 1.f;
+                if (need) {
+                    alpha = ex2((m_ref - m_new) * kLog2e);                // m_ref = -inf -> 0
+                    m_ref = m_new;
+                }
+                if (j > 0 && __any_sync(0xffffffffu, need)) {
+                    // PV of the previous block finished before this block's S was committed.
+#pragma unroll
+                    for (int c = 0; c < D / 32; ++c) {
+                        uint32_t o[32];
+                        tmem_ld32(tO + c * 32, o);
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+                        tmem_st32(tO + c * 32, o);
                     }
                 }
-                if (c + 2 < 4) load_mask32(mk[c & 1], mrow, col0 + (c + 2) * 32, p.mask_cols, row_ok);
+
+                // pass 2: p = 2^((x - m_ref) * log2 e), fp32 row sum, P rounded to the input dtype
+                const float m_use = (m_ref == -INFINITY) ? 0.f : m_ref;
+                const float2 l2e2 = make_float2(kLog2e, kLog2e);
+                const float2 nm2 = make_float2(-m_use * kLog2e, -m_use * kLog2e);
+                float2 sum_a = make_float2(0.f, 0.f), sum_b = make_float2(0.f, 0.f);
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    uint32_t pk[16];
+#pragma unroll
+                    for (int i = 0; i < 16; i += 2) {
+                        const float2 e0 = __ffma2_rn(x[c * 16 + i], l2e2, nm2);
+                        const float2 e1 = __ffma2_rn(x[c * 16 + i + 1], l2e2, nm2);
+                        const float2 p0 = make_float2(ex2(e0.x), ex2(e0.y));
+                        const float2 p1 = make_float2(ex2(e1.x), ex2(e1.y));
+                        sum_a = __fadd2_rn(sum_a, p0);
+                        sum_b = __fadd2_rn(sum_b, p1);
+                        pk[i] = pack2<BF16>(p0.x, p0.y);
+                        pk[i + 1] = pack2<BF16>(p1.x, p1.y);
+                    }
+                    tmem_st16(tS + c * 16, pk);
+                }
+                l = l * alpha + ((sum_a.x + sum_a.y) + (sum_b.x + sum_b.y));
+                tmem_wait_st();
+                tc_fence_before();
+                mbar_arrive(bar_p);
             }
 
-            // reference maximum moves only when the row maximum grew by more than 2^8
-            const float m_new = fmaxf(m_ref, mt);
-            const bool need = (m_new - m_ref) > kRescaleThreshold;   // NaN (-inf - -inf) -> false
-            float alpha = 1.f;
-            if (need) {
-                alpha = ex2(m_ref - m_new);                          // m_ref = -inf -> 0
-                m_ref = m_new;
+            // ---- epilogue: O / l, to the output dtype (or fp32 partial + LSE when split)
+            if (alive) {
+                bool ok = mbar_wait(bar_o_full + 8 * t, 0, abort_flag, p.status, kStSoftmaxO);
+                alive = __all_sync(0xffffffffu, ok);
             }
-            if (j > 0 && __any_sync(0xffffffffu, need)) {
-                // PV of the previous block finished before this block's S was committed.
+            if (alive) {
+                tc_fence_after();
+                const float inv = (l == 0.f || l != l) ? 1.f : (1.f / l);
+                const float lse_val = (l > 0.f) ? m_ref + __logf(l) : -INFINITY;
+                const long long grow = (static_cast<long long>(b) * p.H + h) * p.Sq + row;
+                const bool split_out = p.num_splits > 1;
+                float* o32 = nullptr;
+                if (split_out) {
+                    const long long prow =
+                        ((static_cast<long long>(split) * p.B + b) * p.H + h) * p.Sq + row;
+                    o32 = p.o_part + prow * D;
+                    if (row_ok) p.lse_part[prow] = lse_val;
+                } else {
+                    if (p.out_fp32) o32 = static_cast<float*>(p.out) + grow * D;
+                    if (row_ok && p.lse != nullptr) p.lse[grow] = lse_val;
+                }
+                uint16_t* o16 = static_cast<uint16_t*>(p.out) + grow * D;
 #pragma unroll
                 for (int c = 0; c < D / 32; ++c) {
                     uint32_t o[32];
                     tmem_ld32(tO + c * 32, o);
+                    if (row_ok) {
+                        if (o32 != nullptr) {
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
-                    tmem_st32(tO + c * 32, o);
-                }
-            }
-
-            // pass 2: p = 2^(x - m_ref), fp32 row sum, P rounded to the input dtype
-            const float m_use = (m_ref == -INFINITY) ? 0.f : m_ref;
-            float sum0 = 0.f, sum1 = 0.f, sum2 = 0.f, sum3 = 0.f;
+                            for (int i = 0; i < 32; i += 4) {
+                                float4 f;
+                                f.x = __uint_as_float(o[i]) * inv;
+                                f.y = __uint_as_float(o[i + 1]) * inv;
+                                f.z = __uint_as_float(o[i + 2]) * inv;
+                                f.w = __uint_as_float(o[i + 3]) * inv;
+                                *reinterpret_cast<float4*>(o32 + c * 32 + i) = f;
+                            }
+                        } else {
 #pragma unroll
-            for (int c = 0; c < 4; ++c) {
-                uint32_t pk[16];
-#pragma unroll
-                for (int i = 0; i < 16; i += 2) {
-                    const float p0 = ex2(x[c * 32 + 2 * i] - m_use);
-                    const float p1 = ex2(x[c * 32 + 2 * i + 1] - m_use);
-                    const float p2 = ex2(x[c * 32 + 2 * i + 2] - m_use);
-                    const float p3 = ex2(x[c * 32 + 2 * i + 3] - m_use);
-                    sum0 += p0; sum1 += p1; sum2 += p2; sum3 += p3;
-                    pk[i] = pack2<BF16>(p0, p1);
-                    pk[i + 1] = pack2<BF16>(p2, p3);
-                }
-                tmem_st16(tS + c * 16, pk);
-            }
-            l = l * alpha + ((sum0 + sum1) + (sum2 + sum3));
-            tmem_wait_st();
-            tc_fence_before();
-            mbar_arrive(bar_p);
-        }
-
-        // ---- epilogue: O / l, to the output dtype (or fp32 partial + LSE when split)
-        if (alive) {
-            bool ok = mbar_wait(bar_o_full + 8 * t, 0, abort_flag, p.status, kStSoftmaxO);
-            alive = __all_sync(0xffffffffu, ok);
-        }
-        if (alive) {
-            tc_fence_after();
-            const float inv = (l == 0.f || l != l) ? 1.f : (1.f / l);
-            const float lse_val = (l > 0.f) ? (m_ref + lg2(l)) * kLn2 : -INFINITY;
-            const long long grow = (static_cast<long long>(b) * p.H + h) * p.Sq + row;
-            const bool split_out = p.num_splits > 1;
-            float* o32 = nullptr;
-            if (split_out) {
-                const long long prow =
-                    ((static_cast<long long>(split) * p.B + b) * p.H + h) * p.Sq + row;
-                o32 = p.o_part + prow * D;
-                if (row_ok) p.lse_part[prow] = lse_val;
-            } else {
-                if (p.out_fp32) o32 = static_cast<float*>(p.out) + grow * D;
-                if (row_ok && p.lse != nullptr) p.lse[grow] = lse_val;
-            }
-            uint16_t* o16 = static_cast<uint16_t*>(p.out) + grow * D;
-#pragma unroll
-            for (int c = 0; c < D / 32; ++c) {
-                uint32_t o[32];
-                tmem_ld32(tO + c * 32, o);
-                if (row_ok) {
-                    if (o32 != nullptr) {
-#pragma unroll
-                        for (int i = 0; i < 32; i += 4) {
-                            float4 f;
-                            f.x = __uint_as_float(o[i]) * inv;
-                            f.y = __uint_as_float(o[i + 1]) * inv;
-                            f.z = __uint_as_float(o[i + 2]) * inv;
-                            f.w = __uint_as_float(o[i + 3]) * inv;
-                            *reinterpret_cast<float4*>(o32 + c * 32 + i) = f;
-                        }
-                    } else {
-#pragma unroll
-                        for (int i = 0; i < 32; i += 8) {
-                            uint4 u;
-                            u.x = pack2<BF16>(__uint_as_float(o[i]) * inv, __uint_as_float(o[i + 1]) * inv);
-                            u.y = pack2<BF16>(__uint_as_float(o[i + 2]) * inv, __uint_as_float(o[i + 3]) * inv);
-                            u.z = pack2<BF16>(__uint_as_float(o[i + 4]) * inv, __uint_as_float(o[i + 5]) * inv);
-                            u.w = pack2<BF16>(__uint_as_float(o[i + 6]) * inv, __uint_as_float(o[i + 7]) * inv);
-                            *reinterpret_cast<uint4*>(o16 + c * 32 + i) = u;
+                            for (int i = 0; i < 32; i += 8) {
+                                uint4 u;
+                                u.x = pack2<BF16>(__uint_as_float(o[i]) * inv, __uint_as_float(o[i + 1]) * inv);
+                                u.y = pack2<BF16>(__uint_as_float(o[i + 2]) * inv, __uint_as_float(o[i + 3]) * inv);
+                                u.z = pack2<BF16>(__uint_as_float(o[i + 4]) * inv, __uint_as_float(o[i + 5]) * inv);
+                                u.w = pack2<BF16>(__uint_as_float(o[i + 6]) * inv, __uint_as_float(o[i + 7]) * inv);
+                                *reinterpret_cast<uint4*>(o16 + c * 32 + i) = u;
+                            }
                         }
                     }
                 }
@@ -740,12 +784,16 @@ static int get_encode() {
     return FA_SM100_OK;
 }
 
-// (planes, rows, d) row-major 16-bit tensor, boxes of 128 rows x 64 columns, 128B swizzle.
-static int encode_map(CUtensorMap* tm, const void* ptr, int dtype, int planes, int rows, int d) {
-    const cuuint64_t dims[3] = {static_cast<cuuint64_t>(d), static_cast<cuuint64_t>(rows),
+// (planes, rows, cols) 16-bit tensor with element pitches `row_pitch` and `plane_pitch`,
+// read in boxes of 128 rows x 64 columns with the 128-byte swizzle.
+static int encode_map(CUtensorMap* tm, const void* ptr, int dtype, int planes, int rows, int cols,
+                      long long row_pitch, long long plane_pitch) {
+    const cuuint64_t dims[3] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows),
                                 static_cast<cuuint64_t>(planes)};
-    const cuuint64_t strides[2] = {static_cast<cuuint64_t>(d) * 2,
-                                   static_cast<cuuint64_t>(rows) * d * 2};
+    // A single plane still needs a legal (multiple of 16 bytes, non-zero) outer stride.
+    if (plane_pitch <= 0) plane_pitch = static_cast<long long>(rows) * row_pitch;
+    const cuuint64_t strides[2] = {static_cast<cuuint64_t>(row_pitch) * 2,
+                                   static_cast<cuuint64_t>(plane_pitch) * 2};
     const cuuint32_t box[3] = {64, 128, 1};
     const cuuint32_t estr[3] = {1, 1, 1};
     const CUresult r = g_encode(
@@ -758,7 +806,8 @@ static int encode_map(CUtensorMap* tm, const void* ptr, int dtype, int planes, i
 
 template <int D, bool BF16>
 static int launch_fwd(DeviceInfo* dev, int slot, const CUtensorMap& tq, const CUtensorMap& tk,
-                      const CUtensorMap& tv, const KParams& kp, dim3 grid, cudaStream_t stream) {
+                      const CUtensorMap& tv, const CUtensorMap& tm, const KParams& kp, dim3 grid,
+                      cudaStream_t stream) {
     auto kern = fa_mask_fwd_kernel<D, BF16>;
     if (!dev->attr_set[slot]) {
         if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -768,7 +817,7 @@ static int launch_fwd(DeviceInfo* dev, int slot, const CUtensorMap& tq, const CU
         }
         dev->attr_set[slot] = true;
     }
-    kern<<<grid, kThreads, Cfg<D>::kSmemBytes, stream>>>(tq, tk, tv, kp);
+    kern<<<grid, kThreads, Cfg<D>::kSmemBytes, stream>>>(tq, tk, tv, tm, kp);
     if (cudaGetLastError() != cudaSuccess) return FA_SM100_ERR_CUDA;
     return FA_SM100_OK;
 }
@@ -850,23 +899,21 @@ static int forward(const FaMaskFwdArgs* a, void* workspace, size_t workspace_byt
     }
     KParams kp;
     std::memset(&kp, 0, sizeof(kp));
+    // The mask reaches the kernel through TMA, which wants a 16-byte aligned base and
+    // pitches that are multiples of 16 bytes; anything else is re-pitched first.
+    const uint16_t* mask_ptr = static_cast<const uint16_t*>(a->mask);
+    long long mask_bs = a->mask_batch_stride;
+    long long mask_rs = a->mask_row_stride;
     if (plan.mask_repitched) {
         const int pitch = (a->seqlen_k + 7) & ~7;
         uint16_t* dst = reinterpret_cast<uint16_t*>(ws);
         const unsigned blocks = static_cast<unsigned>(a->batch) * a->seqlen_q;
         fa_mask_repitch_kernel<<<blocks, 256, 0, stream>>>(
-            static_cast<const uint16_t*>(a->mask), dst, a->seqlen_q, a->seqlen_k, pitch,
-            a->mask_batch_stride, a->mask_row_stride);
+            mask_ptr, dst, a->seqlen_q, a->seqlen_k, pitch, mask_bs, mask_rs);
         if (cudaGetLastError() != cudaSuccess) return FA_SM100_ERR_CUDA;
-        kp.mask = dst;
-        kp.mask_bs = static_cast<long long>(a->seqlen_q) * pitch;
-        kp.mask_rs = pitch;
-        kp.mask_cols = pitch;
-    } else {
-        kp.mask = static_cast<const uint16_t*>(a->mask);
-        kp.mask_bs = a->mask_batch_stride;
-        kp.mask_rs = a->mask_row_stride;
-        kp.mask_cols = (a->seqlen_k + 7) & ~7;
+        mask_ptr = dst;
+        mask_bs = static_cast<long long>(a->seqlen_q) * pitch;
+        mask_rs = pitch;
     }
     kp.out = a->out;
     kp.lse = a->lse;
@@ -878,21 +925,27 @@ static int forward(const FaMaskFwdArgs* a, void* workspace, size_t workspace_byt
     kp.blocks_per_split = plan.blocks_per_split;
     kp.kv_blocks = plan.kv_blocks;
     kp.out_fp32 = a->out_fp32;
-    kp.scale_log2 = static_cast<float>(1.4426950408889634 / std::sqrt(static_cast<double>(d)));
+    kp.scale = static_cast<float>(1.0 / std::sqrt(static_cast<double>(d)));
 
-    CUtensorMap tq, tk, tv;
-    if ((rc = encode_map(&tq, a->q, a->dtype, a->batch * a->heads, a->seqlen_q, d)) != FA_SM100_OK) return rc;
-    if ((rc = encode_map(&tk, a->k, a->dtype, a->batch * a->heads_k, a->seqlen_k, d)) != FA_SM100_OK) return rc;
-    if ((rc = encode_map(&tv, a->v, a->dtype, a->batch * a->heads_k, a->seqlen_k, d)) != FA_SM100_OK) return rc;
+    CUtensorMap tq, tk, tv, tm;
+    if ((rc = encode_map(&tq, a->q, a->dtype, a->batch * a->heads, a->seqlen_q, d,
+                         static_cast<long long>(d), static_cast<long long>(a->seqlen_q) * d)) != FA_SM100_OK) return rc;
+    if ((rc = encode_map(&tk, a->k, a->dtype, a->batch * a->heads_k, a->seqlen_k, d,
+                         static_cast<long long>(d), static_cast<long long>(a->seqlen_k) * d)) != FA_SM100_OK) return rc;
+    if ((rc = encode_map(&tv, a->v, a->dtype, a->batch * a->heads_k, a->seqlen_k, d,
+                         static_cast<long long>(d), static_cast<long long>(a->seqlen_k) * d)) != FA_SM100_OK) return rc;
+    // mask: (batch, Sq rows, Sk columns); reads beyond either extent return 0
+    if ((rc = encode_map(&tm, mask_ptr, a->dtype, a->batch, a->seqlen_q, a->seqlen_k, mask_rs,
+                         mask_bs)) != FA_SM100_OK) return rc;
 
     const dim3 grid(plan.grid_x, plan.grid_y, plan.grid_z);
     const bool bf16 = a->dtype == FA_SM100_BF16;
     if (d == 128) {
-        rc = bf16 ? launch_fwd<128, true>(dev, 0, tq, tk, tv, kp, grid, stream)
-                  : launch_fwd<128, false>(dev, 1, tq, tk, tv, kp, grid, stream);
+        rc = bf16 ? launch_fwd<128, true>(dev, 0, tq, tk, tv, tm, kp, grid, stream)
+                  : launch_fwd<128, false>(dev, 1, tq, tk, tv, tm, kp, grid, stream);
     } else {
-        rc = bf16 ? launch_fwd<64, true>(dev, 2, tq, tk, tv, kp, grid, stream)
-                  : launch_fwd<64, false>(dev, 3, tq, tk, tv, kp, grid, stream);
+        rc = bf16 ? launch_fwd<64, true>(dev, 2, tq, tk, tv, tm, kp, grid, stream)
+                  : launch_fwd<64, false>(dev, 3, tq, tk, tv, tm, kp, grid, stream);
     }
     if (rc != FA_SM100_OK) return rc;
     if (plan.num_splits > 1)
