@@ -394,7 +394,9 @@ fa_mask_fwd_kernel(const __grid_constant__ CUtensorMap tm_q,
                 if (!__all_sync(0xffffffffu, ok)) { alive = false; break; }
                 tc_fence_after();
 
-                // pass 1: x = s*scale + mask, block maximum
+                // pass 1: x = s*scale + mask for the whole 128-key block, block maximum
+                uint32_t sreg[kBlockN];
+                tmem_ld128(tS, sreg);
                 float2 x[kBlockN / 2];
                 float mt0 = -INFINITY, mt1 = -INFINITY;
 #pragma unroll
@@ -402,32 +404,43 @@ fa_mask_fwd_kernel(const __grid_constant__ CUtensorMap tm_q,
                     ok = mbar_wait(bar_m_full + 8 * (2 * t + pn), j & 1, abort_flag, p.status,
                                    kStSoftmaxMask);
                     if (!__all_sync(0xffffffffu, ok)) { alive = false; break; }
-                    uint32_t s[64];
-                    tmem_ld64(tS + pn * 64, s);
 #pragma unroll
                     for (int c = 0; c < 8; ++c) {
                         const uint4 mv = lds128(m_row_addr + pn * kPanelBytes +
                                                 ((static_cast<uint32_t>(c) << 4) ^ m_xor));
                         const uint32_t w[4] = {mv.x, mv.y, mv.z, mv.w};
 #pragma unroll
-                        for (int q = 0; q < 4; ++q) {
-                            const int i = c * 8 + q * 2;                  // column inside the panel
-                            const float2 mk = unpack2<BF16>(w[q]);
-                            const float2 sv = make_float2(__uint_as_float(s[i]), __uint_as_float(s[i + 1]));
-                            float2 xv = __ffma2_rn(sv, scale2, mk);
-                            if (tail) {
-                                const int cc = col0 + pn * 64 + i;
-                                if (cc >= p.Sk) xv.x = -INFINITY;
-                                if (cc + 1 >= p.Sk) xv.y = -INFINITY;
-                            }
-                            x[pn * 32 + c * 4 + q] = xv;
-                            mt0 = fmaxf(mt0, xv.x);
-                            mt1 = fmaxf(mt1, xv.y);
+                        for (int q = 0; q < 4; q += 2) {
+                            const int i = pn * 64 + c * 8 + q * 2;        // column inside the block
+                            const float2 xa = __ffma2_rn(
+                                make_float2(__uint_as_float(sreg[i]), __uint_as_float(sreg[i + 1])),
+                                scale2, unpack2<BF16>(w[q]));
+                            const float2 xb = __ffma2_rn(
+                                make_float2(__uint_as_float(sreg[i + 2]), __uint_as_float(sreg[i + 3])),
+                                scale2, unpack2<BF16>(w[q + 1]));
+                            x[i / 2] = xa;
+                            x[i / 2 + 1] = xb;
+                            mt0 = max3(mt0, xa.x, xb.x);
+                            mt1 = max3(mt1, xa.y, xb.y);
                         }
                     }
                     mbar_arrive(bar_m_empty + 8 * (2 * t + pn));      // panel may be refilled
                 }
                 if (!alive) break;
+                if (tail) {
+                    // Last key block of a ragged Sk: columns >= Sk are masked whatever the
+                    // mask tile holds there.  Kept out of the main loop on purpose.
+                    mt0 = -INFINITY;
+                    mt1 = -INFINITY;
+#pragma unroll
+                    for (int i = 0; i < kBlockN / 2; ++i) {
+                        const int cc = col0 + 2 * i;
+                        if (cc >= p.Sk) x[i].x = -INFINITY;
+                        if (cc + 1 >= p.Sk) x[i].y = -INFINITY;
+                        mt0 = fmaxf(mt0, x[i].x);
+                        mt1 = fmaxf(mt1, x[i].y);
+                    }
+                }
                 const float mt = fmaxf(mt0, mt1);
 
                 // reference maximum moves only when the row maximum grew by more than 2^8
