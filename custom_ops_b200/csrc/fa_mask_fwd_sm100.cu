@@ -60,6 +60,16 @@ constexpr int kMmaWarp = 8;
 constexpr int kTmaWarp = 9;
 constexpr int kMaskWarp = 10;
 constexpr int kThreads = 384;
+// Register re-balancing.  The kernel starts with kLaunchRegs per thread (what 384 threads
+// leave of the 64K-register file: the allocation is per scheduler, three warps each).
+// setmaxnreg.inc can only take what setmaxnreg.dec released inside the same CTA, and it
+// blocks until that is there, so the books must balance or the softmax warps wait forever.
+constexpr int kLaunchRegs = 168;
+constexpr int kSoftmaxRegs = 224;
+constexpr int kOtherRegs = 56;
+static_assert(8 * (kSoftmaxRegs - kLaunchRegs) <= 4 * (kLaunchRegs - kOtherRegs),
+              "setmaxnreg.inc would ask for more registers than setmaxnreg.dec releases");
+static_assert(kThreads * kLaunchRegs <= 65536, "launch register budget");
 constexpr uint32_t kTmemCols = 512;
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kRescaleThreshold = 5.545177444479562f;   // 8 * ln 2: rescale when max grew > 2^8
@@ -93,6 +103,7 @@ struct KParams {
     unsigned int* status;
     int B, H, Hk, Sq, Sk;
     int num_splits, blocks_per_split, kv_blocks;
+    int m_pairs;              // 256-row query pairs per (batch, head)
     int out_fp32;
     float scale;              // 1 / sqrt(d)
 };
@@ -154,10 +165,14 @@ fa_mask_fwd_kernel(const __grid_constant__ CUtensorMap tm_q,
     __syncthreads();
     if (s_bail != 0) return;
 
-    const int split = blockIdx.x % p.num_splits;
-    const int mpair = blockIdx.x / p.num_splits;
-    const int h = blockIdx.y;
-    const int b = blockIdx.z;
+    // Work decode: blockIdx.x enumerates (split, 256-row query pair, head, batch), split fastest.
+    int unit = blockIdx.x;
+    const int split = unit % p.num_splits;
+    unit /= p.num_splits;
+    const int mpair = unit % p.m_pairs;
+    unit /= p.m_pairs;
+    const int h = unit % p.H;
+    const int b = unit / p.H;
     const int hk = h / (p.H / p.Hk);
     const int m0 = mpair * (2 * kBlockM);
     const bool has_q1 = (m0 + kBlockM) < p.Sq;
@@ -198,7 +213,7 @@ fa_mask_fwd_kernel(const __grid_constant__ CUtensorMap tm_q,
 
     if (warp >= 8) {
         // Data-movement and MMA-issue warps need few registers; hand the rest to softmax.
-        reg_dealloc<56>();
+        reg_dealloc<kOtherRegs>();
         if (warp == kTmaWarp) {
             // -------------------------------------------------------------- Q/K/V producer
             if (lane == 0) {
@@ -363,7 +378,7 @@ fa_mask_fwd_kernel(const __grid_constant__ CUtensorMap tm_q,
             }
         }
     } else {
-        reg_alloc<224>();
+        reg_alloc<kSoftmaxRegs>();
         if (warp < 4 || has_q1) {
             // -------------------------------------------------------------- softmax groups
             const int t = warp >> 2;
@@ -763,9 +778,14 @@ static int make_plan(const FaMaskFwdArgs* a, FaMaskFwdPlan* plan) {
     plan->kv_blocks = nb;
     plan->blocks_per_split = bps;
     plan->q_tiles_per_cta = a->seqlen_q > kBlockM ? 2 : 1;
-    plan->grid_x = m_pairs * splits;
-    plan->grid_y = a->heads;
-    plan->grid_z = a->batch;
+    // One CTA per unit of (split, 256-row query pair, head, batch).  Splitting the units of a
+    // half-empty last round into single-tile CTAs was measured and gains nothing: a CTA's time
+    // is set by the per-tile softmax -> MMA dependency chain, not by how many tiles it holds.
+    const long long units = static_cast<long long>(m_pairs) * splits * a->heads * a->batch;
+    if (units > 0x3fffffffLL) return FA_SM100_ERR_SHAPE;
+    plan->grid_x = static_cast<int32_t>(units);
+    plan->grid_y = 1;
+    plan->grid_z = 1;
     plan->threads = kThreads;
     plan->smem_bytes = static_cast<int32_t>(d == 128 ? Cfg<128>::kSmemBytes : Cfg<64>::kSmemBytes);
     plan->sm_count = dev->sm_count;
@@ -823,6 +843,13 @@ static int launch_fwd(DeviceInfo* dev, int slot, const CUtensorMap& tq, const CU
                       cudaStream_t stream) {
     auto kern = fa_mask_fwd_kernel<D, BF16>;
     if (!dev->attr_set[slot]) {
+        // The in-kernel register re-balancing is only sound for the register count it was
+        // written for; refuse to launch a build that came out different.
+        cudaFuncAttributes fattr;
+        if (cudaFuncGetAttributes(&fattr, kern) != cudaSuccess || fattr.numRegs != kLaunchRegs) {
+            cudaGetLastError();
+            return FA_SM100_ERR_CUDA;
+        }
         if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  static_cast<int>(Cfg<D>::kSmemBytes)) != cudaSuccess) {
             cudaGetLastError();
@@ -937,6 +964,7 @@ static int forward(const FaMaskFwdArgs* a, void* workspace, size_t workspace_byt
     kp.num_splits = plan.num_splits;
     kp.blocks_per_split = plan.blocks_per_split;
     kp.kv_blocks = plan.kv_blocks;
+    kp.m_pairs = ceil_div(a->seqlen_q, 2 * kBlockM);
     kp.out_fp32 = a->out_fp32;
     kp.scale = static_cast<float>(1.0 / std::sqrt(static_cast<double>(d)));
 

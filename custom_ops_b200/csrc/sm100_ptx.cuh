@@ -66,10 +66,10 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
     return ok != 0;
 }
 
-// Upper bound on polls of one wait.  A poll of try_wait suspends for a
-// hardware-chosen interval (well under a microsecond up to a few), so this is a
-// bound of the order of a second, far above any legitimate wait in these kernels.
-constexpr uint32_t kMaxPolls = 1u << 20;
+// Upper bound of one wait, in SM clock cycles (about 0.1 s): far above any legitimate
+// wait in these kernels, short enough that a broken launch drains in seconds.
+constexpr long long kMaxWaitCycles = 200000000LL;
+constexpr uint32_t kMaxPolls = 1u << 16;     // cap for the drain loops that have no clock check
 
 // Bounded wait.  `abort_flag` is a CTA-shared word: once any role of the CTA gave
 // up, every other wait of that CTA returns at once so the CTA drains and exits.
@@ -77,9 +77,13 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity,
                                           volatile uint32_t* abort_flag,
                                           unsigned int* status, uint32_t code) {
     if (mbar_try_wait(bar, parity)) return true;
-    for (uint32_t i = 0; i < kMaxPolls; ++i) {
+    const long long t0 = clock64();
+    for (uint32_t i = 0;; ++i) {
         if (mbar_try_wait(bar, parity)) return true;
-        if ((i & 63u) == 63u && *abort_flag) return false;
+        if ((i & 31u) == 31u) {
+            if (*abort_flag) return false;
+            if (clock64() - t0 > kMaxWaitCycles) break;
+        }
     }
     *abort_flag = 1;
     atomicMax(status, code);
@@ -199,6 +203,16 @@ __device__ __forceinline__ uint4 lds128(uint32_t saddr) {
                  : "r"(saddr)
                  : "memory");
     return v;
+}
+
+__device__ __forceinline__ uint32_t lds32(uint32_t saddr) {
+    uint32_t v;
+    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(saddr) : "memory");
+    return v;
+}
+
+__device__ __forceinline__ void sts32(uint32_t saddr, uint32_t v) {
+    asm volatile("st.shared.u32 [%0], %1;" ::"r"(saddr), "r"(v) : "memory");
 }
 
 // Register re-balancing between warpgroups (all four warps of a warpgroup execute it).

@@ -92,7 +92,7 @@ typedef struct FaMaskFwdPlan {
     int32_t kv_blocks;          /* number of 128-key blocks */
     int32_t blocks_per_split;
     int32_t q_tiles_per_cta;    /* 128-row query tiles handled by one CTA */
-    int32_t grid_x, grid_y, grid_z;
+    int32_t grid_x, grid_y, grid_z;   /* one-dimensional: grid_y = grid_z = 1 */
     int32_t threads;
     int32_t smem_bytes;
     int32_t mask_repitched;     /* 1 when the mask is first copied to an aligned pitch */

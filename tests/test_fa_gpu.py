@@ -282,3 +282,21 @@ def test_cabi_rejects_bad_arguments_on_device():
         a = _cabi.make_args(**{**good, "seqlen_k": 4096, "mask_seqlen_k": 4096, "num_splits": 4})
         _cabi.forward(a, 0, 0, 0)
     assert e.value.code == -6
+
+
+def test_cross_gpu_splitkv_entry_on_one_rank():
+    """parallel.splitkv_forward with a one-rank NCCL group: local fp32 partial + LSE,
+    gather, merge kernel -- the same calls the multi-GPU path makes."""
+    import torch.distributed as dist
+    from custom_ops_b200 import parallel
+    import socket
+    s = socket.socket(); s.bind(("127.0.0.1", 0)); port = s.getsockname()[1]; s.close()
+    dist.init_process_group("nccl", init_method=f"tcp://127.0.0.1:{port}", rank=0, world_size=1,
+                            device_id=torch.device("cuda", 0))
+    try:
+        q, k, v, m = _cuda(*make_case(1, 4, 4, 128, 2048, 128, torch.bfloat16, "drop_bias", seed=15))
+        out = parallel.splitkv_forward(q, k, v, m)
+        torch.cuda.synchronize()
+        check_against_oracle(out, q, k, v, m, "splitkv_forward")
+    finally:
+        dist.destroy_process_group()

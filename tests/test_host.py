@@ -1,0 +1,204 @@
+"""CPU-only tests of the host side: the C-ABI library loads and exports what the
+header declares, the launch planner and argument validation, the Python mirror of
+the reference's loader/facade, and the workload generators.  No kernel is launched."""
+import ctypes
+import os
+import re
+
+import numpy as np
+import pytest
+import torch
+
+from custom_ops_b200 import _cabi, workloads
+from custom_ops_b200.workloads import WORKLOADS, make_inputs
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+# ------------------------------------------------------------------ C ABI
+def test_library_exports_every_declared_symbol():
+    header = open(os.path.join(ROOT, "include", "fa_mask_fwd_sm100.h")).read()
+    declared = set(re.findall(r"\b(fa_mask_fwd_sm100\w*)\s*\(", header))
+    assert declared == set(_cabi.EXPORTS)
+    lib = _cabi.load()
+    for name in declared:
+        assert getattr(lib, name) is not None
+    assert lib.fa_mask_fwd_sm100_abi_version() == _cabi.ABI_VERSION
+
+
+def test_struct_sizes_match_header_layout():
+    # 2*4 + 6*8 + 8*4 + 2*8 + 4*4 = 120 ; 12*4 + 8 = 56
+    assert ctypes.sizeof(_cabi.FaMaskFwdArgs) == 120
+    assert ctypes.sizeof(_cabi.FaMaskFwdPlan) == 56
+    a = _cabi.make_args(batch=1, heads=1, heads_k=1, seqlen_q=8, seqlen_k=8, head_dim=64,
+                        dtype=_cabi.BF16)
+    a.struct_size = 64
+    with pytest.raises(_cabi.FaSm100Error) as e:
+        _cabi.plan(a)
+    assert e.value.code == -11
+
+
+def _plan(**kw):
+    base = dict(batch=1, heads=1, heads_k=1, seqlen_q=128, seqlen_k=128, head_dim=128,
+                dtype=_cabi.BF16)
+    base.update(kw)
+    return _cabi.plan(_cabi.make_args(**base))
+
+
+def test_plan_of_the_five_configurations():
+    sm = _plan().sm_count                      # 148 where no device can be queried
+    p = _plan(batch=4, heads=16, heads_k=16, seqlen_q=2048, seqlen_k=2048)
+    assert (p.num_splits, p.kv_blocks, p.grid_x, p.q_tiles_per_cta) == (1, 16, 8 * 16 * 4, 2)
+    assert p.workspace_bytes == 0 and p.mask_repitched == 0 and p.threads == 384
+    p = _plan(batch=1, heads=16, heads_k=16, seqlen_q=128, seqlen_k=32768)
+    assert p.kv_blocks == 256 and p.num_splits == max(1, sm // 16) and p.q_tiles_per_cta == 1
+    assert p.blocks_per_split * p.num_splits >= 256 > p.blocks_per_split * (p.num_splits - 1)
+    rows = 16 * 128
+    assert p.workspace_bytes >= p.num_splits * rows * (128 + 1) * 4
+    p = _plan(batch=4, heads=16, heads_k=4, seqlen_q=1000, seqlen_k=4099, dtype=_cabi.FP16)
+    assert p.num_splits == 1 and p.kv_blocks == 33 and p.mask_repitched == 1
+    assert p.workspace_bytes >= 4 * 1000 * 4104 * 2
+    p = _plan(batch=2, heads=4, heads_k=4, seqlen_q=256, seqlen_k=256, head_dim=64)
+    assert p.num_splits == 1 and p.grid_x == 8
+    assert p.smem_bytes <= 232448
+
+
+def test_plan_split_rules():
+    # never an empty split, never more splits than key blocks, forced counts honoured
+    for sk, forced in [(1300, 3), (1300, 7), (1300, 40), (1300, 128), (4096, 40), (130, 2)]:
+        p = _plan(seqlen_k=sk, num_splits=forced)
+        nb = (sk + 127) // 128
+        assert 1 <= p.num_splits <= min(forced, nb)
+        assert (p.num_splits - 1) * p.blocks_per_split < nb <= p.num_splits * p.blocks_per_split
+    assert _plan(seqlen_k=8192, num_splits=1).num_splits == 1
+    assert _plan(seqlen_k=512).num_splits == 1          # too short to be worth splitting
+    assert _plan(seqlen_k=0).num_splits == 1
+
+
+@pytest.mark.parametrize("kw,code", [
+    (dict(dtype=2), -2), (dict(head_dim=96), -4), (dict(heads=6, heads_k=4), -3),
+    (dict(seqlen_q=-1), -3), (dict(mask_seqlen_k=64), -3), (dict(mask_seqlen_q=64), -3),
+    (dict(num_splits=129), -9), (dict(num_splits=-1), -9), (dict(heads_k=0), -3),
+    (dict(mask_row_stride=100), -3),
+])
+def test_validation_codes(kw, code):
+    with pytest.raises(_cabi.FaSm100Error) as e:
+        _plan(**kw)
+    assert e.value.code == code
+    assert _cabi.strerror(code) not in ("ok", "unknown error")
+
+
+def test_null_arguments_and_strerror():
+    lib = _cabi.load()
+    assert lib.fa_mask_fwd_sm100_plan(None, None) == -1
+    n = ctypes.c_size_t()
+    assert lib.fa_mask_fwd_sm100_workspace_bytes(None, ctypes.byref(n)) == -1
+    assert _cabi.strerror(0) == "ok"
+    assert "head_dim" in _cabi.strerror(-4)
+    assert "float16 or bfloat16" in _cabi.strerror(-2)
+    assert _cabi.strerror(-12345) == "unknown error"
+
+
+def test_forward_without_a_gpu_fails_loudly():
+    """No CPU fallback: on a machine without a device the call returns an error."""
+    if torch.cuda.is_available():
+        pytest.skip("a GPU is present")
+    buf = (ctypes.c_uint8 * 4096)()
+    addr = (ctypes.addressof(buf) + 15) & ~15
+    a = _cabi.make_args(q=addr, k=addr, v=addr, mask=addr, out=addr, batch=1, heads=1, heads_k=1,
+                        seqlen_q=8, seqlen_k=8, head_dim=64, dtype=_cabi.BF16)
+    with pytest.raises(_cabi.FaSm100Error) as e:
+        _cabi.forward(a, addr, 4096, 0)
+    assert e.value.code in (-7, -8)
+
+
+# ------------------------------------------------------------------ loader / facade
+def test_group_definition_matches_reference_contract():
+    from custom_ops_b200 import FAOps
+    assert FAOps.namespace == "recsys_ops"
+    assert FAOps.so_name == "recsys_fa_kernel"
+    assert FAOps.required_ops == ["mha_fwd_with_mask"]
+    assert FAOps.fake_ops == ["mha_fwd_with_mask"]
+    assert FAOps.op_schemas["mha_fwd_with_mask"] == \
+        "mha_fwd_with_mask(Tensor q, Tensor k, Tensor v, Tensor mask) -> Tensor"
+    assert FAOps.requires_cuda is True
+
+
+def test_facade_lazy_load_schema_and_fake_kernel():
+    import custom_ops_b200
+    from custom_ops_b200 import RecsysOps
+    fresh = RecsysOps()
+    assert fresh.groups == {"fa": "not_loaded"}
+    assert fresh.load_error() is None
+    fresh.ensure_loaded("fa")
+    assert fresh.groups == {"fa": "loaded"}, fresh.load_error("fa")
+    assert fresh.is_available("fa")
+    schema = str(torch._C._get_schema("recsys_ops::mha_fwd_with_mask", ""))
+    assert schema == "recsys_ops::mha_fwd_with_mask(Tensor q, Tensor k, Tensor v, Tensor mask) -> Tensor"
+    assert torch._C._dispatch_has_kernel_for_dispatch_key("recsys_ops::mha_fwd_with_mask", "Meta")
+    q = torch.empty(2, 4, 10, 64, device="meta", dtype=torch.float16)
+    kv = torch.empty(2, 2, 24, 64, device="meta", dtype=torch.float16)
+    m = torch.empty(2, 1, 10, 24, device="meta", dtype=torch.float16)
+    out = torch.ops.recsys_ops.mha_fwd_with_mask(q, kv, kv, m)
+    assert out.shape == q.shape and out.dtype == q.dtype
+    # a second facade shares the already loaded library
+    again = RecsysOps(allow_jit=False).ensure_loaded("fa")
+    assert again.is_available("fa")
+    assert custom_ops_b200.ops.mha_fwd_with_mask.__doc__
+
+
+def test_facade_errors():
+    from custom_ops_b200 import CustomOpsError, RecsysOps
+    ops = RecsysOps()
+    x = torch.zeros(1, 1, 8, 64, dtype=torch.bfloat16)
+    m = torch.zeros(1, 1, 8, 8, dtype=torch.bfloat16)
+    with pytest.raises(RuntimeError, match="only supported on CUDA"):
+        ops.mha_fwd_with_mask(x, x, x, m)                  # CPU tensors: the reference's stub message
+    with pytest.raises(CustomOpsError):
+        ops.mha_fwd_with_mask(x, x, x, m, backend="tilelang")
+    with pytest.raises(ValueError):
+        ops.mha_fwd_with_mask(x, x, x, m, backend="rocm")
+    with pytest.raises(AttributeError):
+        ops.fuse_moe
+    with pytest.raises(ValueError):
+        ops.is_available("moe")
+
+
+def test_strict_mode_does_not_build(tmp_path, monkeypatch):
+    from custom_ops_b200 import FAOps
+    g = FAOps(allow_jit=False)
+    monkeypatch.setattr(g, "prebuilt_path", lambda: str(tmp_path / "missing.so"))
+    with pytest.warns(UserWarning):
+        g.load()
+    assert not g.is_available()
+    assert "allow_jit=False" in g.load_error()
+    with pytest.raises(RuntimeError, match="extension not loaded"):
+        g.mha_fwd_with_mask
+
+
+# ------------------------------------------------------------------ workloads
+def test_workload_shapes_flops_bytes():
+    w = WORKLOADS["standard"]
+    assert w.flops == 4 * 4 * 16 * 2048 * 2048 * 128 == 137438953472
+    assert w.bytes == 167772160
+    assert WORKLOADS["splitkv_long"].bytes == pytest.approx(277.87e6, rel=1e-3)
+    assert WORKLOADS["ragged_items"].dtype == torch.float16
+
+
+def test_mask_recipes():
+    g = torch.Generator().manual_seed(0)
+    m = workloads.make_mask("random10", 2, 64, 64, torch.bfloat16, g)
+    frac = torch.isneginf(m.float()).float().mean().item()
+    assert 0.05 < frac < 0.15
+    assert torch.all(m[:, 0].diagonal(dim1=-2, dim2=-1) == 0)
+    m = workloads.make_mask("causal_window", 1, 1024, 1024, torch.bfloat16, g)[0, 0]
+    assert m[600, 600] == 0 and m[600, 89] == 0 and torch.isneginf(m[600, 88]) and torch.isneginf(m[600, 601])
+    m = workloads.make_mask("padding_random", 1, 8, 1000, torch.bfloat16, g)[0, 0]
+    assert torch.isneginf(m[:, 900:].float()).all() and (m[:, 0] == 0).all()
+    m = workloads.make_mask("item_sparse", 1, 16, 83, torch.float16, g)[0, 0]
+    assert (m[:, :64] == 0).all()
+    items = torch.isneginf(m[:, 64:80].float()).view(16, 2, 8)
+    assert (items.all(-1) | (~items).all(-1)).all()        # whole 8-token items
+    q, k, v, mm = make_inputs(workloads.small_analogue(WORKLOADS["ragged_items"], 20, 83, H=8))
+    assert q.shape == (1, 8, 20, 128) and k.shape == (1, 2, 83, 128) and mm.shape == (1, 1, 20, 83)
+    assert abs(q.float().std().item() - 0.5) < 0.05
