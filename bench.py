@@ -110,7 +110,10 @@ class ClockSampler:
             for n, v in zip(names, parts[3:7]):
                 if v.lower().startswith("active"):
                     reasons.add(n)
-        return {"sm_mhz": statistics.median(sm) if sm else None,
+        # the idle samples before the first launch sit at the idle clock; the median under
+        # load is taken over the upper half of the samples
+        sm_load = sorted(sm)[len(sm) // 2:] if len(sm) > 3 else sm
+        return {"sm_mhz": statistics.median(sm_load) if sm_load else None,
                 "sm_max_mhz": max(smax) if smax else None,
                 "samples": len(sm), "reasons": sorted(reasons)}
 
@@ -282,13 +285,17 @@ def run_ours(args, w):
     if not ops.is_available("fa"):
         raise SystemExit(f"operator library failed to load: {ops.load_error('fa')}")
 
-    for _ in range(max(3, args.warmup)):
-        step_kernel()
-    torch.cuda.synchronize(dev)
-
+    # clocks are sampled from before the warm-up to after the last timed step
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
+        t_wait = time.time()
+        while not sampler.lines and time.time() - t_wait < 3.0:
+            time.sleep(0.05)
+
+    for _ in range(max(3, args.warmup)):
+        step_kernel()
+    torch.cuda.synchronize(dev)
 
     # ---- timed region 1: kernel-only, inputs resident in HBM
     starts = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]

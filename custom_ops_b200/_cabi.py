@@ -73,7 +73,7 @@ class FaMaskFwdPlan(ctypes.Structure):
         ("smem_bytes", ctypes.c_int32),
         ("mask_repitched", ctypes.c_int32),
         ("sm_count", ctypes.c_int32),
-        ("reserved", ctypes.c_int32),
+        ("dual_split", ctypes.c_int32),
         ("workspace_bytes", ctypes.c_uint64),
     ]
 

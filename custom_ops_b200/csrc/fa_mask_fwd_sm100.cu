@@ -102,8 +102,10 @@ struct KParams {
     float* lse_part;          // (splits, B, H, Sq)
     unsigned int* status;
     int B, H, Hk, Sq, Sk;
-    int num_splits, blocks_per_split, kv_blocks;
+    int num_splits, kv_blocks;
     int m_pairs;              // 256-row query pairs per (batch, head)
+    int split_groups;         // CTAs along the split axis: num_splits, or ceil(num_splits/2) in dual mode
+    int dual;                 // 1: one query tile, two KV splits per CTA
     int out_fp32;
     float scale;              // 1 / sqrt(d)
 };
@@ -148,11 +150,11 @@ fa_mask_fwd_kernel(const __grid_constant__ CUtensorMap tm_q,
     const uint32_t bar_o_full = sBar + 48;             // [2]
     const uint32_t bar_m_full = sBar + 64;             // [4]
     const uint32_t bar_m_empty = sBar + 96;            // [4]
-    const uint32_t bar_kv_full = sBar + 128;           // [NS]
-    const uint32_t bar_kv_empty = sBar + 128 + 8 * NS; // [NS]
-    const uint32_t tmem_slot_addr = sBar + 128 + 16 * NS;
+    const uint32_t bar_kv_full = sBar + 128;           // [NS + 1] (dual mode has one slot more)
+    const uint32_t bar_kv_empty = sBar + 128 + 8 * (NS + 1); // [NS + 1]
+    const uint32_t tmem_slot_addr = sBar + 128 + 16 * (NS + 1);
     uint8_t* bar_generic = smem_raw + (sBar - raw_u32);
-    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(bar_generic + 128 + 16 * NS);
+    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(bar_generic + 128 + 16 * (NS + 1));
     volatile uint32_t* abort_flag = tmem_slot + 1;
 
     const int warp = threadIdx.x >> 5;
@@ -165,20 +167,42 @@ fa_mask_fwd_kernel(const __grid_constant__ CUtensorMap tm_q,
     __syncthreads();
     if (s_bail != 0) return;
 
-    // Work decode: blockIdx.x enumerates (split, 256-row query pair, head, batch), split fastest.
+    // Work decode: blockIdx.x enumerates (split group, 256-row query pair, head, batch), split
+    // group fastest.  The CTA runs two independent softmax/MMA streams ("slots"):
+    //   pair mode  slot t = query tile t of the pair; both slots walk the same key blocks and
+    //              share every K/V tile in shared memory;
+    //   dual mode  (one query tile only, Split-KV) slot t = KV split 2*group + t of the SAME
+    //              query tile: two key ranges stream side by side, so a CTA that would
+    //              otherwise leave half of its softmax threads idle pulls twice the bytes.
     int unit = blockIdx.x;
-    const int split = unit % p.num_splits;
-    unit /= p.num_splits;
+    const int sgroup = unit % p.split_groups;
+    unit /= p.split_groups;
     const int mpair = unit % p.m_pairs;
     unit /= p.m_pairs;
     const int h = unit % p.H;
     const int b = unit / p.H;
     const int hk = h / (p.H / p.Hk);
     const int m0 = mpair * (2 * kBlockM);
-    const bool has_q1 = (m0 + kBlockM) < p.Sq;
-    const int nb_begin = split * p.blocks_per_split;
-    const int nb_end = min(p.kv_blocks, nb_begin + p.blocks_per_split);
-    const int n = nb_end - nb_begin;               // >= 1 by construction of the plan
+    const bool dual = p.dual != 0;
+    int sl_split[2], sl_begin[2], sl_n[2], sl_row0[2];
+#pragma unroll
+    for (int t = 0; t < 2; ++t) {
+        sl_split[t] = dual ? 2 * sgroup + t : sgroup;
+        // split s owns key blocks [s*nb/S, (s+1)*nb/S): sizes differ by at most one block
+        sl_begin[t] = static_cast<int>(static_cast<long long>(sl_split[t]) * p.kv_blocks / p.num_splits);
+        sl_row0[t] = dual ? m0 : m0 + t * kBlockM;
+        const int cnt = static_cast<int>(static_cast<long long>(sl_split[t] + 1) * p.kv_blocks /
+                                         p.num_splits) - sl_begin[t];
+        const bool on = dual ? (sl_split[t] < p.num_splits) : (sl_row0[t] < p.Sq);
+        sl_n[t] = (on && cnt > 0) ? cnt : 0;       // slot 0 always has >= 1 block (plan)
+    }
+    const bool has_q1 = !dual && sl_n[1] > 0;
+    const int n = sl_n[0];
+    const int nb_begin = sl_begin[0];
+    const int nmax = max(sl_n[0], sl_n[1]);
+    // dual mode needs one Q tile only: the second Q buffer becomes a fourth K/V ring slot
+    const uint32_t ring_base = dual ? sKV - TILE : sKV;
+    const int ring_slots = dual ? NS + 1 : NS;
 
     if (warp == kTmaWarp && lane == 0) {
         for (int t = 0; t < 2; ++t) {
@@ -191,7 +215,7 @@ fa_mask_fwd_kernel(const __grid_constant__ CUtensorMap tm_q,
             mbar_init(bar_m_full + 8 * i, 1);
             mbar_init(bar_m_empty + 8 * i, kSoftmaxThreads);
         }
-        for (int i = 0; i < NS; ++i) {
+        for (int i = 0; i < NS + 1; ++i) {
             mbar_init(bar_kv_full + 8 * i, 1);
             mbar_init(bar_kv_empty + 8 * i, 1);
         }
@@ -230,29 +254,48 @@ fa_mask_fwd_kernel(const __grid_constant__ CUtensorMap tm_q,
                         tma_load_3d(sQ + TILE + s * SUB, &tm_q, bar_q_full + 8, s * 64,
                                     m0 + kBlockM, q_plane);
                 }
-                const int fills = 2 * n;                // K_0, V_0, K_1, V_1, ...
+                // One K or V tile into the next ring slot; false when a wait gave up.
                 int issued = 0;
-                for (int f = 0; f < fills; ++f) {
-                    const int slot = f % NS;
-                    if (f >= NS &&
-                        !mbar_wait(bar_kv_empty + 8 * slot, ((f / NS) - 1) & 1, abort_flag,
+                auto fill = [&](bool is_v, int block) -> bool {
+                    const int f = issued;
+                    const int slot = f % ring_slots;
+                    if (f >= ring_slots &&
+                        !mbar_wait(bar_kv_empty + 8 * slot, ((f / ring_slots) - 1) & 1, abort_flag,
                                    p.status, kStTmaEmpty))
-                        break;
-                    const int j = f >> 1;
-                    const CUtensorMap* tm = (f & 1) ? &tm_v : &tm_k;
-                    const uint32_t dst = sKV + slot * TILE;
+                        return false;
+                    const CUtensorMap* tm = is_v ? &tm_v : &tm_k;
+                    const uint32_t dst = ring_base + slot * TILE;
                     mbar_arrive_expect_tx(bar_kv_full + 8 * slot, TILE);
 #pragma unroll
                     for (int s = 0; s < C::kSub; ++s)
                         tma_load_3d(dst + s * SUB, tm, bar_kv_full + 8 * slot, s * 64,
-                                    (nb_begin + j) * kBlockN, kv_plane);
+                                    block * kBlockN, kv_plane);
                     issued = f + 1;
+                    return true;
+                };
+                bool ok = true;
+                if (!dual) {
+                    // shared by both slots: K_0, V_0, K_1, V_1, ...
+                    for (int j = 0; ok && j < n; ++j)
+                        ok = fill(false, nb_begin + j) && fill(true, nb_begin + j);
+                } else {
+                    // the order the MMA thread consumes them: K_a0, K_b0, then per step
+                    // V_a(j), K_a(j+1), V_b(j), K_b(j+1)
+                    ok = fill(false, sl_begin[0]);
+                    if (ok && sl_n[1] > 0) ok = fill(false, sl_begin[1]);
+                    for (int j = 0; ok && j < nmax; ++j) {
+#pragma unroll
+                        for (int t = 0; t < 2; ++t) {
+                            if (ok && j < sl_n[t]) ok = fill(true, sl_begin[t] + j);
+                            if (ok && j + 1 < sl_n[t]) ok = fill(false, sl_begin[t] + j + 1);
+                        }
+                    }
                 }
                 if (*abort_flag) {
                     // Giving up: let the copies already in flight land before the CTA exits.
-                    for (int f = max(0, issued - NS); f < issued; ++f) {
-                        const uint32_t bar = bar_kv_full + 8 * (f % NS);
-                        const uint32_t par = (f / NS) & 1;
+                    for (int f = max(0, issued - ring_slots); f < issued; ++f) {
+                        const uint32_t bar = bar_kv_full + 8 * (f % ring_slots);
+                        const uint32_t par = (f / ring_slots) & 1;
                         bool done = false;
                         for (uint32_t i = 0; i < kMaxPolls && !done; ++i) done = mbar_try_wait(bar, par);
                         if (!done) atomicMax(p.status, static_cast<unsigned int>(kStDrain));
@@ -262,12 +305,13 @@ fa_mask_fwd_kernel(const __grid_constant__ CUtensorMap tm_q,
         } else if (warp == kMaskWarp) {
             // -------------------------------------------------------------- mask producer
             if (lane == 0) {
-                const int tiles = has_q1 ? 2 : 1;
-                int last_j = -1;
+                // Panel i = slot * 2 + half.  A slot's panels follow that slot's own key blocks.
+                int last_j[2] = {-1, -1};
                 bool ok = true;
-                for (int j = 0; ok && j < n; ++j) {
-                    const int col0 = (nb_begin + j) * kBlockN;
-                    for (int i = 0; ok && i < 2 * tiles; ++i) {     // i = tile * 2 + panel
+                for (int j = 0; ok && j < nmax; ++j) {
+                    for (int i = 0; ok && i < 4; ++i) {
+                        const int t = i >> 1;
+                        if (j >= sl_n[t]) continue;
                         if (j > 0 && !mbar_wait(bar_m_empty + 8 * i, (j - 1) & 1, abort_flag,
                                                 p.status, kStMaskEmpty)) {
                             ok = false;
@@ -275,15 +319,17 @@ fa_mask_fwd_kernel(const __grid_constant__ CUtensorMap tm_q,
                         }
                         mbar_arrive_expect_tx(bar_m_full + 8 * i, kPanelBytes);
                         tma_load_3d(sM + i * kPanelBytes, &tm_m, bar_m_full + 8 * i,
-                                    col0 + (i & 1) * 64, m0 + (i >> 1) * kBlockM, b);
+                                    (sl_begin[t] + j) * kBlockN + (i & 1) * 64, sl_row0[t], b);
+                        if (i & 1) last_j[t] = j;
                     }
-                    if (ok) last_j = j;
                 }
-                if (*abort_flag && last_j >= 0) {
-                    for (int i = 0; i < 2 * tiles; ++i) {
+                if (*abort_flag) {
+                    for (int i = 0; i < 4; ++i) {
+                        const int lj = last_j[i >> 1];
+                        if (lj < 0) continue;
                         bool done = false;
                         for (uint32_t it = 0; it < kMaxPolls && !done; ++it)
-                            done = mbar_try_wait(bar_m_full + 8 * i, last_j & 1);
+                            done = mbar_try_wait(bar_m_full + 8 * i, lj & 1);
                         if (!done) atomicMax(p.status, static_cast<unsigned int>(kStDrain));
                     }
                 }
@@ -298,10 +344,11 @@ fa_mask_fwd_kernel(const __grid_constant__ CUtensorMap tm_q,
 
                 // S_t = Q_t K^T : A and B both K-major, 64-column 128B-swizzled panels.
                 auto issue_s = [&](int t, uint32_t k_addr) {
+                    const uint32_t q_addr = dual ? sQ : sQ + t * TILE;   // dual: both slots share Q
 #pragma unroll
                     for (int ks = 0; ks < D / 16; ++ks) {
                         const uint32_t off = (ks >> 2) * SUB + (ks & 3) * 32;
-                        const uint64_t da = smem_desc_sw128(sQ + t * TILE + off, 16, 1024);
+                        const uint64_t da = smem_desc_sw128(q_addr + off, 16, 1024);
                         const uint64_t db = smem_desc_sw128(k_addr + off, 16, 1024);
                         mma_ss(tS0 + t * 128, da, db, idesc_s, ks > 0 ? 1u : 0u);
                     }
@@ -318,6 +365,56 @@ fa_mask_fwd_kernel(const __grid_constant__ CUtensorMap tm_q,
                 };
 
                 bool ok = mbar_wait(bar_q_full, 0, abort_flag, p.status, kStMmaQ);
+                if (dual) {
+                    // Two independent streams; every K/V tile belongs to one slot and is
+                    // released as soon as that slot's MMAs are issued.  `f` walks the ring in
+                    // the producer's order.
+                    int f = 0;
+                    auto take = [&](uint32_t& addr) -> bool {
+                        const int slot = f % ring_slots;
+                        const bool got = mbar_wait(bar_kv_full + 8 * slot, (f / ring_slots) & 1,
+                                                   abort_flag, p.status, kStMmaKv);
+                        addr = ring_base + slot * TILE;
+                        return got;
+                    };
+                    auto release = [&]() {
+                        mma_commit(bar_kv_empty + 8 * (f % ring_slots));
+                        ++f;
+                    };
+                    uint32_t addr = 0;
+#pragma unroll
+                    for (int t = 0; t < 2; ++t) {
+                        if (ok && sl_n[t] > 0 && (ok = take(addr))) {
+                            tc_fence_after();
+                            issue_s(t, addr);
+                            mma_commit(bar_s_full + 8 * t);
+                            release();
+                        }
+                    }
+                    for (int j = 0; ok && j < nmax; ++j) {
+#pragma unroll
+                        for (int t = 0; t < 2; ++t) {
+                            if (!ok || j >= sl_n[t]) continue;
+                            if (!(ok = take(addr))) break;                       // V_t(j)
+                            if (!(ok = mbar_wait(bar_p_ready + 8 * t, j & 1, abort_flag, p.status,
+                                                 kStMmaP)))
+                                break;
+                            tc_fence_after();
+                            issue_pv(t, addr, j > 0);
+                            release();
+                            if (j + 1 < sl_n[t]) {
+                                if (!(ok = take(addr))) break;                   // K_t(j+1)
+                                tc_fence_after();
+                                issue_s(t, addr);
+                                mma_commit(bar_s_full + 8 * t);
+                                release();
+                            } else {
+                                mma_commit(bar_o_full + 8 * t);
+                            }
+                        }
+                    }
+                    ok = false;                                                  // pair path below is skipped
+                }
                 ok = ok && mbar_wait(bar_kv_full, 0, abort_flag, p.status, kStMmaKv);
                 if (ok) {
                     tc_fence_after();
@@ -379,12 +476,15 @@ fa_mask_fwd_kernel(const __grid_constant__ CUtensorMap tm_q,
         }
     } else {
         reg_alloc<kSoftmaxRegs>();
-        if (warp < 4 || has_q1) {
+        if (sl_n[warp >> 2] > 0) {
             // -------------------------------------------------------------- softmax groups
             const int t = warp >> 2;
             const int wq = warp & 3;
             const int row_in_tile = wq * 32 + lane;
-            const int row = m0 + t * kBlockM + row_in_tile;
+            const int row = sl_row0[t] + row_in_tile;
+            const int n_t = sl_n[t];
+            const int begin_t = sl_begin[t];
+            const int split = sl_split[t];
             const bool row_ok = row < p.Sq;
             const uint32_t lane_sel = static_cast<uint32_t>(wq * 32) << 16;
             const uint32_t tS = tmem_base + lane_sel + t * 128;
@@ -401,8 +501,8 @@ fa_mask_fwd_kernel(const __grid_constant__ CUtensorMap tm_q,
             float l = 0.f;               // row sum relative to m_ref
             bool alive = true;
 
-            for (int j = 0; j < n; ++j) {
-                const int col0 = (nb_begin + j) * kBlockN;
+            for (int j = 0; j < n_t; ++j) {
+                const int col0 = (begin_t + j) * kBlockN;
                 const bool tail = (col0 + kBlockN) > p.Sk;
 
                 bool ok = mbar_wait(bar_s, j & 1, abort_flag, p.status, kStSoftmaxS);
@@ -772,8 +872,19 @@ static int make_plan(const FaMaskFwdArgs* a, FaMaskFwdPlan* plan) {
         }
         if (splits > nb) splits = nb;
     }
-    int bps = nb > 0 ? ceil_div(nb, splits) : 0;
-    if (nb > 0) splits = ceil_div(nb, bps);          // no empty split
+    // One query tile and a split key range: a CTA takes two splits side by side (dual mode),
+    // so aim for two splits per SM-filling CTA.
+    const bool one_tile = a->seqlen_q <= kBlockM;
+    if (one_tile && splits > 1 && a->num_splits == 0) {
+        long long s2 = 2LL * splits;
+        if (s2 > nb / 4) s2 = nb / 4;
+        if (s2 > FA_SM100_MAX_SPLITS) s2 = FA_SM100_MAX_SPLITS;
+        if (s2 > splits) splits = static_cast<int>(s2);
+    }
+    // split s owns blocks [s*nb/S, (s+1)*nb/S): never empty because S <= nb
+    const int bps = nb > 0 ? ceil_div(nb, splits) : 0;
+    const bool dual = one_tile && splits > 1;
+    const int split_groups = dual ? ceil_div(splits, 2) : splits;
     plan->num_splits = splits;
     plan->kv_blocks = nb;
     plan->blocks_per_split = bps;
@@ -781,11 +892,12 @@ static int make_plan(const FaMaskFwdArgs* a, FaMaskFwdPlan* plan) {
     // One CTA per unit of (split, 256-row query pair, head, batch).  Splitting the units of a
     // half-empty last round into single-tile CTAs was measured and gains nothing: a CTA's time
     // is set by the per-tile softmax -> MMA dependency chain, not by how many tiles it holds.
-    const long long units = static_cast<long long>(m_pairs) * splits * a->heads * a->batch;
+    const long long units = static_cast<long long>(m_pairs) * split_groups * a->heads * a->batch;
     if (units > 0x3fffffffLL) return FA_SM100_ERR_SHAPE;
     plan->grid_x = static_cast<int32_t>(units);
     plan->grid_y = 1;
     plan->grid_z = 1;
+    plan->dual_split = dual ? 1 : 0;
     plan->threads = kThreads;
     plan->smem_bytes = static_cast<int32_t>(d == 128 ? Cfg<128>::kSmemBytes : Cfg<64>::kSmemBytes);
     plan->sm_count = dev->sm_count;
@@ -962,9 +1074,10 @@ static int forward(const FaMaskFwdArgs* a, void* workspace, size_t workspace_byt
     kp.status = dev->status_ptr;
     kp.B = a->batch; kp.H = a->heads; kp.Hk = a->heads_k; kp.Sq = a->seqlen_q; kp.Sk = a->seqlen_k;
     kp.num_splits = plan.num_splits;
-    kp.blocks_per_split = plan.blocks_per_split;
     kp.kv_blocks = plan.kv_blocks;
     kp.m_pairs = ceil_div(a->seqlen_q, 2 * kBlockM);
+    kp.dual = plan.dual_split;
+    kp.split_groups = plan.dual_split ? ceil_div(plan.num_splits, 2) : plan.num_splits;
     kp.out_fp32 = a->out_fp32;
     kp.scale = static_cast<float>(1.0 / std::sqrt(static_cast<double>(d)));
 

@@ -90,14 +90,14 @@ typedef struct FaMaskFwdArgs {
 typedef struct FaMaskFwdPlan {
     int32_t num_splits;         /* KV splits actually used (1 = single pass) */
     int32_t kv_blocks;          /* number of 128-key blocks */
-    int32_t blocks_per_split;
+    int32_t blocks_per_split;   /* largest split; split s owns blocks [s*nb/S, (s+1)*nb/S) */
     int32_t q_tiles_per_cta;    /* 128-row query tiles handled by one CTA */
     int32_t grid_x, grid_y, grid_z;   /* one-dimensional: grid_y = grid_z = 1 */
     int32_t threads;
     int32_t smem_bytes;
     int32_t mask_repitched;     /* 1 when the mask is first copied to an aligned pitch */
     int32_t sm_count;
-    int32_t reserved;
+    int32_t dual_split;         /* 1: one query tile per CTA, two KV splits side by side */
     uint64_t workspace_bytes;
 } FaMaskFwdPlan;
 

@@ -147,7 +147,7 @@ def test_splitkv_forced_counts(splits):
     """Non-power-of-two counts, uneven ranges, more splits asked than key blocks."""
     q, k, v, m = _cuda(*make_case(1, 3, 3, 130, 1300, 128, torch.bfloat16, "drop_bias", seed=7))
     out, lse, plan = run_cabi(q, k, v, m, num_splits=splits, want_lse=True)
-    assert 1 <= plan.num_splits <= min(splits, plan.kv_blocks)
+    assert plan.num_splits == min(splits, plan.kv_blocks)
     check_against_oracle(out, q, k, v, m, f"forced{splits}")
     ref_lse = oracle.lse_fp32(bits(q), bits(k), bits(m), "bf16")
     assert np.abs(lse.cpu().numpy() - ref_lse).max() < 2e-3
@@ -300,3 +300,18 @@ def test_cross_gpu_splitkv_entry_on_one_rank():
         check_against_oracle(out, q, k, v, m, "splitkv_forward")
     finally:
         dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("case", [(128, 1300, 3, 128), (100, 4099, 0, 128), (1, 2048, 5, 64),
+                                  (128, 2048, 2, 64), (77, 1024, 8, 128)])
+def test_splitkv_single_tile_dual_mode(dtype, case):
+    """Sq <= 128 with a split key range: one CTA runs two KV splits side by side
+    (odd split counts leave the last CTA with one)."""
+    sq, sk, splits, d = case
+    q, k, v, m = _cuda(*make_case(1, 3, 1, sq, sk, d, dtype, "drop_bias", seed=16))
+    out, lse, plan = run_cabi(q, k, v, m, num_splits=splits, want_lse=True)
+    assert plan.dual_split == 1 and plan.num_splits >= 2
+    check_against_oracle(out, q, k, v, m, f"dual{case}")
+    ref_lse = oracle.lse_fp32(bits(q), bits(k), bits(m), tag(q))
+    assert np.abs(lse.cpu().numpy() - ref_lse).max() < 2e-3

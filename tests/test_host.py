@@ -51,8 +51,9 @@ def test_plan_of_the_five_configurations():
     assert (p.num_splits, p.kv_blocks, p.grid_x, p.q_tiles_per_cta) == (1, 16, 8 * 16 * 4, 2)
     assert p.workspace_bytes == 0 and p.mask_repitched == 0 and p.threads == 384
     p = _plan(batch=1, heads=16, heads_k=16, seqlen_q=128, seqlen_k=32768)
-    assert p.kv_blocks == 256 and p.num_splits == max(1, sm // 16) and p.q_tiles_per_cta == 1
-    assert p.blocks_per_split * p.num_splits >= 256 > p.blocks_per_split * (p.num_splits - 1)
+    assert p.kv_blocks == 256 and p.num_splits == 2 * max(1, sm // 16) and p.q_tiles_per_cta == 1
+    assert p.dual_split == 1 and p.grid_x == 16 * ((p.num_splits + 1) // 2)
+    assert p.blocks_per_split == -(-256 // p.num_splits)
     rows = 16 * 128
     assert p.workspace_bytes >= p.num_splits * rows * (128 + 1) * 4
     p = _plan(batch=4, heads=16, heads_k=4, seqlen_q=1000, seqlen_k=4099, dtype=_cabi.FP16)
@@ -68,8 +69,8 @@ def test_plan_split_rules():
     for sk, forced in [(1300, 3), (1300, 7), (1300, 40), (1300, 128), (4096, 40), (130, 2)]:
         p = _plan(seqlen_k=sk, num_splits=forced)
         nb = (sk + 127) // 128
-        assert 1 <= p.num_splits <= min(forced, nb)
-        assert (p.num_splits - 1) * p.blocks_per_split < nb <= p.num_splits * p.blocks_per_split
+        assert p.num_splits == min(forced, nb)
+        assert p.blocks_per_split == -(-nb // p.num_splits)
     assert _plan(seqlen_k=8192, num_splits=1).num_splits == 1
     assert _plan(seqlen_k=512).num_splits == 1          # too short to be worth splitting
     assert _plan(seqlen_k=0).num_splits == 1
