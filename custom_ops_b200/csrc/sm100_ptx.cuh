@@ -107,6 +107,16 @@ __device__ __forceinline__ void tma_load_3d(uint32_t dst_smem, const void* tmap,
         : "memory");
 }
 
+// Programmatic dependent launch: let the next kernel in the stream start its prologue /
+// wait until the kernel before has finished and its writes are visible.
+__device__ __forceinline__ void pdl_launch_dependents() {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
+__device__ __forceinline__ void pdl_wait_prior_grid() {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+
 // ----------------------------------------------------------------------------
 // Tensor memory
 // ----------------------------------------------------------------------------
