@@ -27,6 +27,7 @@ EXPORTS = [
     "fa_mask_fwd_sm100_plan",
     "fa_mask_fwd_sm100_workspace_bytes",
     "fa_mask_fwd_sm100",
+    "fa_mask_fwd_sm100_static_scratch",
     "fa_mask_fwd_sm100_combine",
     "fa_mask_fwd_sm100_device_status",
     "fa_mask_fwd_sm100_strerror",
@@ -111,6 +112,8 @@ def load(path: str | None = None):
     lib.fa_mask_fwd_sm100.restype = ctypes.c_int
     lib.fa_mask_fwd_sm100.argtypes = [P(FaMaskFwdArgs), ctypes.c_void_p, ctypes.c_size_t,
                                       ctypes.c_void_p]
+    lib.fa_mask_fwd_sm100_static_scratch.restype = ctypes.c_int
+    lib.fa_mask_fwd_sm100_static_scratch.argtypes = [P(FaMaskFwdArgs), ctypes.c_void_p]
     lib.fa_mask_fwd_sm100_combine.restype = ctypes.c_int
     lib.fa_mask_fwd_sm100_combine.argtypes = [
         ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int32,
@@ -173,6 +176,15 @@ def workspace_bytes(args: FaMaskFwdArgs) -> int:
 def forward(args: FaMaskFwdArgs, workspace: int, workspace_nbytes: int, stream: int):
     check(load().fa_mask_fwd_sm100(ctypes.byref(args), workspace or None, workspace_nbytes,
                                    stream or None))
+
+
+STATIC_SCRATCH_BYTES = 24 * 1024 * 1024
+
+
+def forward_static_scratch(args: FaMaskFwdArgs, stream: int):
+    """The forward on the library's built-in scratch: nothing is allocated anywhere.
+    Calls that may overlap on the GPU must not share it (they would race)."""
+    check(load().fa_mask_fwd_sm100_static_scratch(ctypes.byref(args), stream or None))
 
 
 def combine(o_parts: int, lse_parts: int, out: int, lse_out: int, num_parts: int, rows: int,

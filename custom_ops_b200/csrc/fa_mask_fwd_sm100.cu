@@ -1203,6 +1203,45 @@ static int forward(const FaMaskFwdArgs* a, void* workspace, size_t workspace_byt
     return rc;
 }
 
+// ---------------------------------------------------------------------------------
+// Built-in scratch for callers that cannot allocate device memory.
+// ---------------------------------------------------------------------------------
+// The array below is part of the library image: every GPU on which the library is loaded
+// carries these FA_SM100_STATIC_SCRATCH_BYTES until the process exits.  Its name is only a
+// host-side handle; the device address is looked up once per device with
+// cudaGetSymbolAddress and cached.
+static __device__ __align__(256) unsigned char g_static_scratch[FA_SM100_STATIC_SCRATCH_BYTES];
+static void* g_static_scratch_addr[kMaxDevices] = {};
+static std::mutex g_static_scratch_mutex;
+
+static int forward_static_scratch(const FaMaskFwdArgs* a, cudaStream_t stream) {
+    FaMaskFwdPlan plan;
+    int rc = make_plan(a, &plan);
+    if (rc != FA_SM100_OK) return rc;
+    if (plan.workspace_bytes > FA_SM100_STATIC_SCRATCH_BYTES) return FA_SM100_ERR_WORKSPACE;
+    void* scratch = nullptr;
+    {
+        std::lock_guard<std::mutex> lock(g_static_scratch_mutex);
+        scratch = g_static_scratch_addr[a->device];
+        if (scratch == nullptr) {
+            // set-up, once per device, with that device current
+            DeviceGuard guard(a->device);
+            if (guard.err != cudaSuccess) {
+                cudaGetLastError();
+                return FA_SM100_ERR_CUDA;
+            }
+            void* ptr = nullptr;
+            if (cudaGetSymbolAddress(&ptr, g_static_scratch) != cudaSuccess || ptr == nullptr) {
+                cudaGetLastError();
+                return FA_SM100_ERR_CUDA;
+            }
+            g_static_scratch_addr[a->device] = ptr;
+            scratch = ptr;
+        }
+    }
+    return forward(a, scratch, FA_SM100_STATIC_SCRATCH_BYTES, stream);
+}
+
 }  // namespace fa_sm100
 
 // ---------------------------------------------------------------------------------
@@ -1275,6 +1314,10 @@ int fa_mask_fwd_sm100_device_status(int32_t device, uint32_t* status, int32_t cl
         }
     }
     return v == 0 ? FA_SM100_OK : FA_SM100_ERR_DEVICE_WAIT;
+}
+
+int fa_mask_fwd_sm100_static_scratch(const FaMaskFwdArgs* args, void* stream) {
+    return fa_sm100::forward_static_scratch(args, static_cast<cudaStream_t>(stream));
 }
 
 const char* fa_mask_fwd_sm100_strerror(int code) {

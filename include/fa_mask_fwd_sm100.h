@@ -119,6 +119,32 @@ int fa_mask_fwd_sm100_workspace_bytes(const FaMaskFwdArgs* args, size_t* bytes);
 int fa_mask_fwd_sm100(const FaMaskFwdArgs* args, void* workspace, size_t workspace_bytes,
                       void* stream);
 
+/* Bytes of scratch built into the library for fa_mask_fwd_sm100_static_scratch. */
+#define FA_SM100_STATIC_SCRATCH_BYTES (24u * 1024u * 1024u)
+
+/* The same forward as fa_mask_fwd_sm100, for callers that have no way to hand over scratch
+ * memory: code running where cudaMalloc is off limits (inside a region that is being captured
+ * or replayed, in a latency-critical serving loop that forbids allocator calls, in a host
+ * runtime whose memory pool is owned by someone else), or bindings that can only pass the
+ * operator's own tensors.  It has no counterpart in the reference, whose launcher always
+ * allocates its Split-KV buffers through torch (csrc/fa/fa_fwd_launch.h:289-297).
+ *
+ * Inputs and outputs are still the caller's.  The Split-KV partials, their LSE and a re-pitched
+ * mask go into an array of FA_SM100_STATIC_SCRATCH_BYTES that is part of the library image, so
+ * every GPU the library is loaded on holds that much until the process ends.  A call that
+ * would need more returns FA_SM100_ERR_WORKSPACE and does nothing; nothing is ever allocated
+ * or freed, by this function or by anything it calls.
+ *
+ * The first call on a device looks up the array's device address (cudaGetSymbolAddress, with
+ * that device current) and keeps it; make that first call outside any stream capture.
+ *
+ * There is one array per device and every call uses it from its start: two calls whose GPU
+ * work can overlap (different streams, no ordering between them) race on it and corrupt each
+ * other's result; calls on one stream are safe.  The array keeps whatever the last call left
+ * there; that is harmless because each call writes every scratch word before it reads it --
+ * nothing in it has to start at zero. */
+int fa_mask_fwd_sm100_static_scratch(const FaMaskFwdArgs* args, void* stream);
+
 /* Merges `num_parts` normalised fp32 partial results that cover disjoint key
  * ranges: out = sum_s exp(lse_s - max) * o_s / sum_s exp(lse_s - max), rows whose
  * every lse is -inf give 0.  `o_parts` is (num_parts, rows, head_dim) fp32,
