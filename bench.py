@@ -265,7 +265,8 @@ def run_ours(args, w):
     ws_bytes = _cabi.workspace_bytes(cargs)
     ws = torch.empty(max(ws_bytes, 16), dtype=torch.uint8, device=dev)
     stream = torch.cuda.current_stream(dev)
-    launches_per_step = 1 + (1 if plan.num_splits > 1 else 0) + (1 if plan.mask_repitched else 0)
+    launches_per_step = (1 + (1 if plan.num_splits > 1 else 0) + (1 if plan.mask_repitched else 0)
+                         + (1 if plan.tile_skip else 0))
 
     def step_kernel():
         if cross_split:

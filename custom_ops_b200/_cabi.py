@@ -57,7 +57,7 @@ class FaMaskFwdArgs(ctypes.Structure):
         ("dtype", ctypes.c_int32),
         ("num_splits", ctypes.c_int32),
         ("out_fp32", ctypes.c_int32),
-        ("reserved", ctypes.c_int32),
+        ("no_tile_skip", ctypes.c_int32),
     ]
 
 
@@ -75,6 +75,8 @@ class FaMaskFwdPlan(ctypes.Structure):
         ("mask_repitched", ctypes.c_int32),
         ("sm_count", ctypes.c_int32),
         ("dual_split", ctypes.c_int32),
+        ("tile_skip", ctypes.c_int32),
+        ("reserved", ctypes.c_int32),
         ("workspace_bytes", ctypes.c_uint64),
     ]
 
@@ -142,7 +144,8 @@ def check(code: int):
 
 def make_args(*, q=0, k=0, v=0, mask=0, out=0, lse=0, batch, heads, heads_k, seqlen_q, seqlen_k,
               head_dim, dtype, mask_seqlen_q=None, mask_seqlen_k=None, mask_batch_stride=None,
-              mask_row_stride=None, device=0, num_splits=0, out_fp32=0) -> FaMaskFwdArgs:
+              mask_row_stride=None, device=0, num_splits=0, out_fp32=0,
+              no_tile_skip=0) -> FaMaskFwdArgs:
     a = FaMaskFwdArgs()
     a.struct_size = ctypes.sizeof(FaMaskFwdArgs)
     a.device = device
@@ -158,6 +161,7 @@ def make_args(*, q=0, k=0, v=0, mask=0, out=0, lse=0, batch, heads, heads_k, seq
     a.dtype = dtype
     a.num_splits = num_splits
     a.out_fp32 = out_fp32
+    a.no_tile_skip = no_tile_skip
     return a
 
 

@@ -72,6 +72,7 @@ static_assert(8 * (kSoftmaxRegs - kLaunchRegs) <= 4 * (kLaunchRegs - kOtherRegs)
               "setmaxnreg.inc would ask for more registers than setmaxnreg.dec releases");
 static_assert(kThreads * kLaunchRegs <= 65536, "launch register budget");
 constexpr uint32_t kTmemCols = 512;
+constexpr int kMaxListBlocks = 512;    // key blocks a CTA can keep a skip list for (Sk <= 65536)
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kRescaleThreshold = 5.545177444479562f;   // 8 * ln 2: rescale when max grew > 2^8
 constexpr uint32_t kPanelBytes = 128 * 64 * 2;            // 128 rows x 64 columns, 16 bit
@@ -92,8 +93,9 @@ struct Cfg {
     static constexpr int kSub = D / 64;
     static constexpr uint32_t kMaskBytes = 4 * kPanelBytes;       // 2 tiles x 2 panels
     static constexpr uint32_t kBarBytes = 256;
+    static constexpr uint32_t kListBytes = kMaxListBlocks * 2;   // compacted key-block list (uint16)
     static constexpr uint32_t kSmemBytes =
-        1024 + 2 * kTileBytes + kStages * kTileBytes + kMaskBytes + kBarBytes;
+        1024 + 2 * kTileBytes + kStages * kTileBytes + kMaskBytes + kBarBytes + kListBytes;
 };
 
 struct KParams {
@@ -107,6 +109,8 @@ struct KParams {
     int m_pairs;              // 256-row query pairs per (batch, head)
     int split_groups;         // CTAs along the split axis: num_splits, or ceil(num_splits/2) in dual mode
     int dual;                 // 1: one query tile, two KV splits per CTA
+    const unsigned char* block_flags;   // (B, m_pairs, kv_blocks): 0 = every key of the block is
+                                        // masked (-inf) for all 256 rows -> skipped; NULL = no skipping
     int out_fp32;
     float scale;              // 1 / sqrt(d)
 };
@@ -154,9 +158,12 @@ fa_mask_fwd_kernel(const __grid_constant__ CUtensorMap tm_q,
     const uint32_t bar_kv_full = sBar + 128;           // [NS + 1] (dual mode has one slot more)
     const uint32_t bar_kv_empty = sBar + 128 + 8 * (NS + 1); // [NS + 1]
     const uint32_t tmem_slot_addr = sBar + 128 + 16 * (NS + 1);
+    const uint32_t sList = sBar + C::kBarBytes;          // uint16 [kMaxListBlocks]
     uint8_t* bar_generic = smem_raw + (sBar - raw_u32);
+    volatile uint16_t* blk_list = reinterpret_cast<volatile uint16_t*>(bar_generic + C::kBarBytes);
     volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(bar_generic + 128 + 16 * (NS + 1));
     volatile uint32_t* abort_flag = tmem_slot + 1;
+    volatile int* list_count = reinterpret_cast<volatile int*>(tmem_slot + 2);
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -185,25 +192,25 @@ fa_mask_fwd_kernel(const __grid_constant__ CUtensorMap tm_q,
     const int hk = h / (p.H / p.Hk);
     const int m0 = mpair * (2 * kBlockM);
     const bool dual = p.dual != 0;
-    int sl_split[2], sl_begin[2], sl_n[2], sl_row0[2];
-#pragma unroll
-    for (int t = 0; t < 2; ++t) {
-        sl_split[t] = dual ? 2 * sgroup + t : sgroup;
-        // split s owns key blocks [s*nb/S, (s+1)*nb/S): sizes differ by at most one block
-        sl_begin[t] = static_cast<int>(static_cast<long long>(sl_split[t]) * p.kv_blocks / p.num_splits);
-        sl_row0[t] = dual ? m0 : m0 + t * kBlockM;
-        const int cnt = static_cast<int>(static_cast<long long>(sl_split[t] + 1) * p.kv_blocks /
-                                         p.num_splits) - sl_begin[t];
-        const bool on = dual ? (sl_split[t] < p.num_splits) : (sl_row0[t] < p.Sq);
-        sl_n[t] = (on && cnt > 0) ? cnt : 0;       // slot 0 always has >= 1 block (plan)
+    // Tile skipping (single-pass pair mode only): a pre-pass marked the key blocks whose mask
+    // is -inf for all 256 rows of this pair.  The idle warp compacts the flags into a list of
+    // the blocks to visit; every role then walks the list instead of 0..kv_blocks-1.  Skipping
+    // such a block is exact: all of its weights would be 0.
+    const bool use_list = (p.block_flags != nullptr);
+    if (use_list && warp == 11) {
+        pdl_wait_prior_grid();                 // the flags come from the pre-pass kernel
+        const unsigned char* fl = p.block_flags +
+            (static_cast<long long>(b) * p.m_pairs + mpair) * p.kv_blocks;
+        int count = 0;
+        for (int base_j = 0; base_j < p.kv_blocks; base_j += 32) {
+            const int jj = base_j + lane;
+            const bool need = jj < p.kv_blocks && fl[jj] != 0;
+            const unsigned ballot = __ballot_sync(0xffffffffu, need);
+            if (need) blk_list[count + __popc(ballot & ((1u << lane) - 1u))] = static_cast<uint16_t>(jj);
+            count += __popc(ballot);
+        }
+        if (lane == 0) *list_count = count;
     }
-    const bool has_q1 = !dual && sl_n[1] > 0;
-    const int n = sl_n[0];
-    const int nb_begin = sl_begin[0];
-    const int nmax = max(sl_n[0], sl_n[1]);
-    // dual mode needs one Q tile only: the second Q buffer becomes a fourth K/V ring slot
-    const uint32_t ring_base = dual ? sKV - TILE : sKV;
-    const int ring_slots = dual ? NS + 1 : NS;
 
     if (warp == kTmaWarp && lane == 0) {
         for (int t = 0; t < 2; ++t) {
@@ -237,6 +244,32 @@ fa_mask_fwd_kernel(const __grid_constant__ CUtensorMap tm_q,
     const uint32_t tmem_base = *tmem_slot;
     pdl_launch_dependents();      // a chained merge kernel may start its prologue now
 
+    int sl_split[2], sl_begin[2], sl_n[2], sl_row0[2];
+    bool sl_on[2];
+#pragma unroll
+    for (int t = 0; t < 2; ++t) {
+        sl_split[t] = dual ? 2 * sgroup + t : sgroup;
+        // split s owns key blocks [s*nb/S, (s+1)*nb/S): sizes differ by at most one block
+        sl_begin[t] = static_cast<int>(static_cast<long long>(sl_split[t]) * p.kv_blocks / p.num_splits);
+        sl_row0[t] = dual ? m0 : m0 + t * kBlockM;
+        const int cnt = static_cast<int>(static_cast<long long>(sl_split[t] + 1) * p.kv_blocks /
+                                         p.num_splits) - sl_begin[t];
+        sl_on[t] = dual ? (sl_split[t] < p.num_splits) : (sl_row0[t] < p.Sq);
+        sl_n[t] = (sl_on[t] && cnt > 0) ? cnt : 0;
+        if (use_list) sl_n[t] = sl_on[t] ? *list_count : 0;   // may be 0: nothing visible at all
+    }
+    // key block visited at step j of slot t
+    auto blk = [&](int t, int j) -> int {
+        return use_list ? static_cast<int>(blk_list[j]) : sl_begin[t] + j;
+    };
+    const bool has_q1 = !dual && sl_n[1] > 0;
+    const int n = sl_n[0];
+    const int nmax = max(sl_n[0], sl_n[1]);
+    // dual mode needs one Q tile only: the second Q buffer becomes a fourth K/V ring slot
+    const uint32_t ring_base = dual ? sKV - TILE : sKV;
+    const int ring_slots = dual ? NS + 1 : NS;
+
+
     if (warp >= 8) {
         // Data-movement and MMA-issue warps need few registers; hand the rest to softmax.
         reg_dealloc<kOtherRegs>();
@@ -245,10 +278,12 @@ fa_mask_fwd_kernel(const __grid_constant__ CUtensorMap tm_q,
             if (lane == 0) {
                 const int q_plane = b * p.H + h;
                 const int kv_plane = b * p.Hk + hk;
-                mbar_arrive_expect_tx(bar_q_full, TILE);
+                if (n > 0) {
+                    mbar_arrive_expect_tx(bar_q_full, TILE);
 #pragma unroll
-                for (int s = 0; s < C::kSub; ++s)
-                    tma_load_3d(sQ + s * SUB, &tm_q, bar_q_full, s * 64, m0, q_plane);
+                    for (int s = 0; s < C::kSub; ++s)
+                        tma_load_3d(sQ + s * SUB, &tm_q, bar_q_full, s * 64, m0, q_plane);
+                }
                 if (has_q1) {
                     mbar_arrive_expect_tx(bar_q_full + 8, TILE);
 #pragma unroll
@@ -279,7 +314,7 @@ fa_mask_fwd_kernel(const __grid_constant__ CUtensorMap tm_q,
                 if (!dual) {
                     // shared by both slots: K_0, V_0, K_1, V_1, ...
                     for (int j = 0; ok && j < n; ++j)
-                        ok = fill(false, nb_begin + j) && fill(true, nb_begin + j);
+                        ok = fill(false, blk(0, j)) && fill(true, blk(0, j));
                 } else {
                     // the order the MMA thread consumes them: K_a0, K_b0, then per step
                     // V_a(j), K_a(j+1), V_b(j), K_b(j+1)
@@ -307,6 +342,10 @@ fa_mask_fwd_kernel(const __grid_constant__ CUtensorMap tm_q,
         } else if (warp == kMaskWarp) {
             // -------------------------------------------------------------- mask producer
             if (lane == 0) {
+                // The mask may be a re-pitched copy written by the kernel launched just before
+                // this one (chained with programmatic dependent launch): wait for it here, so
+                // everything that does not need the mask has already started.
+                pdl_wait_prior_grid();
                 // Panel i = slot * 2 + half.  A slot's panels follow that slot's own key blocks.
                 int last_j[2] = {-1, -1};
                 bool ok = true;
@@ -321,7 +360,7 @@ fa_mask_fwd_kernel(const __grid_constant__ CUtensorMap tm_q,
                         }
                         mbar_arrive_expect_tx(bar_m_full + 8 * i, kPanelBytes);
                         tma_load_3d(sM + i * kPanelBytes, &tm_m, bar_m_full + 8 * i,
-                                    (sl_begin[t] + j) * kBlockN + (i & 1) * 64, sl_row0[t], b);
+                                    blk(t, j) * kBlockN + (i & 1) * 64, sl_row0[t], b);
                         if (i & 1) last_j[t] = j;
                     }
                 }
@@ -366,7 +405,7 @@ fa_mask_fwd_kernel(const __grid_constant__ CUtensorMap tm_q,
                     }
                 };
 
-                bool ok = mbar_wait(bar_q_full, 0, abort_flag, p.status, kStMmaQ);
+                bool ok = (n > 0) && mbar_wait(bar_q_full, 0, abort_flag, p.status, kStMmaQ);
                 if (dual) {
                     // Two independent streams; every K/V tile belongs to one slot and is
                     // released as soon as that slot's MMAs are issued.  `f` walks the ring in
@@ -478,14 +517,13 @@ fa_mask_fwd_kernel(const __grid_constant__ CUtensorMap tm_q,
         }
     } else {
         reg_alloc<kSoftmaxRegs>();
-        if (sl_n[warp >> 2] > 0) {
+        if (sl_on[warp >> 2]) {
             // -------------------------------------------------------------- softmax groups
             const int t = warp >> 2;
             const int wq = warp & 3;
             const int row_in_tile = wq * 32 + lane;
             const int row = sl_row0[t] + row_in_tile;
             const int n_t = sl_n[t];
-            const int begin_t = sl_begin[t];
             const int split = sl_split[t];
             const bool row_ok = row < p.Sq;
             const uint32_t lane_sel = static_cast<uint32_t>(wq * 32) << 16;
@@ -504,7 +542,7 @@ fa_mask_fwd_kernel(const __grid_constant__ CUtensorMap tm_q,
             bool alive = true;
 
             for (int j = 0; j < n_t; ++j) {
-                const int col0 = (begin_t + j) * kBlockN;
+                const int col0 = blk(t, j) * kBlockN;
                 const bool tail = (col0 + kBlockN) > p.Sk;
 
                 bool ok = mbar_wait(bar_s, j & 1, abort_flag, p.status, kStSoftmaxS);
@@ -608,7 +646,10 @@ fa_mask_fwd_kernel(const __grid_constant__ CUtensorMap tm_q,
             }
 
             // ---- epilogue: O / l, to the output dtype (or fp32 partial + LSE when split)
-            if (alive) {
+            // (a slot whose every key block was skipped has nothing in tensor memory: its rows
+            // are fully masked, the result is 0 and the LSE -inf)
+            const bool empty = (n_t == 0);
+            if (alive && !empty) {
                 bool ok = mbar_wait(bar_o_full + 8 * t, 0, abort_flag, p.status, kStSoftmaxO);
                 alive = __all_sync(0xffffffffu, ok);
             }
@@ -632,7 +673,12 @@ fa_mask_fwd_kernel(const __grid_constant__ CUtensorMap tm_q,
 #pragma unroll
                 for (int c = 0; c < D / 32; ++c) {
                     uint32_t o[32];
-                    tmem_ld32(tO + c * 32, o);
+                    if (!empty) {
+                        tmem_ld32(tO + c * 32, o);
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) o[i] = 0u;
+                    }
                     if (row_ok) {
                         if (o32 != nullptr) {
 #pragma unroll
@@ -772,6 +818,50 @@ fa_mask_combine_kernel(const float* __restrict__ o_parts, const float* __restric
 }
 
 // ---------------------------------------------------------------------------------
+// Tile-skip pre-pass: one CTA per (key block, 256-row query pair, batch) decides whether the
+// mask holds anything but -inf in that 256 x 128 region (only rows < Sq and columns < Sk
+// count).  flag = 1: the block must be visited; 0: every weight in it would be 0.
+// The mask rows are 16-byte aligned here (the launcher re-pitches otherwise).  A CTA stops
+// reading at the first pass that saw a visible entry, so a mask without all-masked regions
+// costs a few kilobytes per CTA.
+// ---------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256)
+fa_mask_classify_kernel(const uint16_t* __restrict__ mask, long long bs, long long rs, int Sq, int Sk,
+                        uint32_t neg_inf2, unsigned char* __restrict__ flags) {
+    const int nt = blockIdx.x, mp = blockIdx.y, b = blockIdx.z;
+    pdl_wait_prior_grid();                          // a re-pitch kernel may have written the mask
+    pdl_launch_dependents();
+    const int vec = threadIdx.x & 15;               // 16 vectors of 8 keys per 128-key row piece
+    const int rsub = threadIdx.x >> 4;              // 16 rows per pass
+    const int col = nt * kBlockN + vec * 8;
+    const uint16_t neg_inf = static_cast<uint16_t>(neg_inf2 & 0xffffu);
+    int visible = 0;
+    for (int pass = 0; pass < 2 * kBlockM / 16; ++pass) {
+        const int row = mp * 2 * kBlockM + pass * 16 + rsub;
+        if (row < Sq && col < Sk) {
+            const uint16_t* src = mask + b * bs + row * rs + col;
+            const uint4 v = __ldg(reinterpret_cast<const uint4*>(src));
+            if (col + 8 <= Sk) {
+                visible |= (v.x != neg_inf2) | (v.y != neg_inf2) | (v.z != neg_inf2) | (v.w != neg_inf2);
+            } else {
+                const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+                for (int e = 0; e < 8; ++e) {
+                    const uint16_t x = static_cast<uint16_t>(w[e >> 1] >> ((e & 1) * 16));
+                    if (col + e < Sk && x != neg_inf) visible = 1;
+                }
+            }
+        }
+        if (__syncthreads_or(visible)) {
+            visible = 1;
+            break;
+        }
+    }
+    if (threadIdx.x == 0)
+        flags[(static_cast<long long>(b) * gridDim.y + mp) * gridDim.x + nt] = visible ? 1 : 0;
+}
+
+// ---------------------------------------------------------------------------------
 // Mask re-pitch: copies the (Sq, Sk) corner of each batch's mask to a pitch that is
 // a multiple of 8 elements so every row starts on a 16-byte boundary.  Pad columns
 // get 0; the attention kernel masks columns >= Sk itself.
@@ -779,6 +869,7 @@ fa_mask_combine_kernel(const float* __restrict__ o_parts, const float* __restric
 __global__ void __launch_bounds__(256)
 fa_mask_repitch_kernel(const uint16_t* __restrict__ src, uint16_t* __restrict__ dst, int Sq, int Sk,
                        int pitch, long long src_bs, long long src_rs) {
+    pdl_launch_dependents();
     const long long r = blockIdx.x;                  // b * Sq + row
     const int b = static_cast<int>(r / Sq);
     const int row = static_cast<int>(r % Sq);
@@ -936,6 +1027,10 @@ static int make_plan(const FaMaskFwdArgs* a, FaMaskFwdPlan* plan) {
         const size_t pitch = (a->seqlen_k + 7) & ~7;
         ws += align256(static_cast<size_t>(a->batch) * a->seqlen_q * pitch * 2);
     }
+    // Tile skipping: single pass over the keys, at least two key blocks, list fits the CTA.
+    plan->tile_skip = (splits == 1 && nb >= 4 && nb <= kMaxListBlocks && a->seqlen_q > 0 &&
+                       a->no_tile_skip == 0) ? 1 : 0;
+    if (plan->tile_skip) ws += align256(static_cast<size_t>(a->batch) * m_pairs * nb);
     plan->workspace_bytes = ws;
     return FA_SM100_OK;
 }
@@ -1023,7 +1118,7 @@ static int get_maps(const MapKey& key, CUtensorMap* tq, CUtensorMap* tk, CUtenso
 template <int D, bool BF16>
 static int launch_fwd(DeviceInfo* dev, int slot, const CUtensorMap& tq, const CUtensorMap& tk,
                       const CUtensorMap& tv, const CUtensorMap& tm, const KParams& kp, dim3 grid,
-                      cudaStream_t stream) {
+                      cudaStream_t stream, bool chained) {
     auto kern = fa_mask_fwd_kernel<D, BF16>;
     if (!dev->attr_set[slot]) {
         // The in-kernel register re-balancing is only sound for the register count it was
@@ -1039,6 +1134,24 @@ static int launch_fwd(DeviceInfo* dev, int slot, const CUtensorMap& tq, const CU
             return FA_SM100_ERR_CUDA;
         }
         dev->attr_set[slot] = true;
+    }
+    if (chained) {
+        // behind a pre-pass kernel: start this kernel's prologue under that kernel's tail
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = grid;
+        cfg.blockDim = dim3(kThreads);
+        cfg.dynamicSmemBytes = Cfg<D>::kSmemBytes;
+        cfg.stream = stream;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        if (cudaLaunchKernelEx(&cfg, kern, tq, tk, tv, tm, kp) != cudaSuccess) {
+            cudaGetLastError();
+            return FA_SM100_ERR_CUDA;
+        }
+        return FA_SM100_OK;
     }
     kern<<<grid, kThreads, Cfg<D>::kSmemBytes, stream>>>(tq, tk, tv, tm, kp);
     if (cudaGetLastError() != cudaSuccess) return FA_SM100_ERR_CUDA;
@@ -1164,6 +1277,27 @@ static int forward(const FaMaskFwdArgs* a, void* workspace, size_t workspace_byt
         mask_bs = static_cast<long long>(a->seqlen_q) * pitch;
         mask_rs = pitch;
     }
+    if (plan.tile_skip) {
+        unsigned char* flags = ws + (plan.mask_repitched
+            ? align256(static_cast<size_t>(a->batch) * a->seqlen_q * ((a->seqlen_k + 7) & ~7) * 2) : 0);
+        const dim3 cgrid(plan.kv_blocks, ceil_div(a->seqlen_q, 2 * kBlockM), a->batch);
+        const uint32_t ninf = a->dtype == FA_SM100_BF16 ? 0xFF80FF80u : 0xFC00FC00u;
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = cgrid;
+        cfg.blockDim = dim3(256);
+        cfg.stream = stream;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = plan.mask_repitched ? 1 : 0;      // chained behind the re-pitch kernel
+        if (cudaLaunchKernelEx(&cfg, fa_mask_classify_kernel, mask_ptr, mask_bs, mask_rs, a->seqlen_q,
+                               a->seqlen_k, ninf, flags) != cudaSuccess) {
+            cudaGetLastError();
+            return FA_SM100_ERR_CUDA;
+        }
+        kp.block_flags = flags;
+    }
     kp.out = a->out;
     kp.lse = a->lse;
     kp.o_part = o_part;
@@ -1188,13 +1322,14 @@ static int forward(const FaMaskFwdArgs* a, void* workspace, size_t workspace_byt
     if ((rc = get_maps(key, &tq, &tk, &tv, &tm)) != FA_SM100_OK) return rc;
 
     const dim3 grid(plan.grid_x, plan.grid_y, plan.grid_z);
+    const bool chained = plan.mask_repitched || plan.tile_skip;
     const bool bf16 = a->dtype == FA_SM100_BF16;
     if (d == 128) {
-        rc = bf16 ? launch_fwd<128, true>(dev, 0, tq, tk, tv, tm, kp, grid, stream)
-                  : launch_fwd<128, false>(dev, 1, tq, tk, tv, tm, kp, grid, stream);
+        rc = bf16 ? launch_fwd<128, true>(dev, 0, tq, tk, tv, tm, kp, grid, stream, chained)
+                  : launch_fwd<128, false>(dev, 1, tq, tk, tv, tm, kp, grid, stream, chained);
     } else {
-        rc = bf16 ? launch_fwd<64, true>(dev, 2, tq, tk, tv, tm, kp, grid, stream)
-                  : launch_fwd<64, false>(dev, 3, tq, tk, tv, tm, kp, grid, stream);
+        rc = bf16 ? launch_fwd<64, true>(dev, 2, tq, tk, tv, tm, kp, grid, stream, chained)
+                  : launch_fwd<64, false>(dev, 3, tq, tk, tv, tm, kp, grid, stream, chained);
     }
     if (rc != FA_SM100_OK) return rc;
     if (plan.num_splits > 1)

@@ -83,7 +83,7 @@ typedef struct FaMaskFwdArgs {
     int32_t dtype;              /* FA_SM100_FP16 / FA_SM100_BF16 */
     int32_t num_splits;         /* 0 = choose, 1 = never split, n = force n KV splits */
     int32_t out_fp32;           /* 1: `out` is fp32 (normalised partial for a cross-GPU merge) */
-    int32_t reserved;
+    int32_t no_tile_skip;       /* 1: visit every key block even where the mask hides it entirely */
 } FaMaskFwdArgs;
 
 /* What the launcher decided for a set of arguments; for tests and tuning. */
@@ -98,6 +98,8 @@ typedef struct FaMaskFwdPlan {
     int32_t mask_repitched;     /* 1 when the mask is first copied to an aligned pitch */
     int32_t sm_count;
     int32_t dual_split;         /* 1: one query tile per CTA, two KV splits side by side */
+    int32_t tile_skip;          /* 1: a pre-pass finds key blocks masked for a whole 256-row pair; they are skipped */
+    int32_t reserved;
     uint64_t workspace_bytes;
 } FaMaskFwdPlan;
 

@@ -315,3 +315,47 @@ def test_splitkv_single_tile_dual_mode(dtype, case):
     check_against_oracle(out, q, k, v, m, f"dual{case}")
     ref_lse = oracle.lse_fp32(bits(q), bits(k), bits(m), tag(q))
     assert np.abs(lse.cpu().numpy() - ref_lse).max() < 2e-3
+
+
+# ---------------------------------------------------------------- tile skipping
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("case", [(2, 4, 2, 768, 768, 128, 160), (1, 2, 2, 1000, 1411, 64, 300),
+                                  (1, 2, 1, 300, 2053, 128, 512)])
+def test_tile_skipping_is_exact_on_structured_masks(dtype, case):
+    """Causal-and-window masks leave most 256x128 regions fully masked.  Skipping them must
+    not change a single bit relative to visiting them (their weights are exactly 0), and
+    both must match the oracle."""
+    b, h, hk, sq, sk, d, window = case
+    q, k, v, _ = make_case(b, h, hk, sq, sk, d, dtype, "zero", seed=17)
+    i = torch.arange(sq).view(sq, 1)
+    j = torch.arange(sk).view(1, sk)
+    vis = (i + (sk - sq) - j >= 0) & (i + (sk - sq) - j < window)
+    m = torch.zeros(sq, sk).masked_fill(~vis, float("-inf")).to(dtype)
+    m = m.view(1, 1, sq, sk).expand(b, 1, sq, sk).contiguous()
+    q, k, v, m = _cuda(q, k, v, m)
+    out_skip, lse_skip, plan = run_cabi(q, k, v, m, want_lse=True, num_splits=1)
+    out_all, lse_all, plan_all = run_cabi(q, k, v, m, want_lse=True, num_splits=1, no_tile_skip=1)
+    assert plan.tile_skip == 1 and plan_all.tile_skip == 0
+    assert torch.equal(out_skip, out_all)
+    assert torch.equal(lse_skip, lse_all)
+    check_against_oracle(out_skip, q, k, v, m, f"skip{case}")
+
+
+def test_tile_skipping_everything_masked_and_trap_columns():
+    """(a) a whole 256-row pair with no visible key at all: output 0, LSE -inf, no block is
+    visited; (b) the only 'visible' entries of a region sit in columns >= Sk of a pre-padded
+    mask: they do not count."""
+    q, k, v, m = make_case(1, 2, 2, 512, 640, 128, torch.bfloat16, "drop_bias", seed=18)
+    m[:, :, 256:, :] = float("-inf")
+    q, k, v, m = _cuda(q, k, v, m)
+    out, lse, plan = run_cabi(q, k, v, m, want_lse=True, num_splits=1)
+    assert plan.tile_skip == 1
+    assert torch.all(out[:, :, 256:] == 0) and torch.all(torch.isneginf(lse[:, :, 256:]))
+    check_against_oracle(out, q, k, v, m, "all-masked pair")
+    q, k, v, m = make_case(1, 2, 2, 200, 700, 64, torch.float16, "zero", seed=19, pad_cols=12)
+    m[:, :, :, 256:] = float("-inf")
+    m[:, :, :, 700:] = 0.0                      # trap: visible-looking values beyond Sk
+    q, k, v, m = _cuda(q, k, v, m)
+    out, _, plan = run_cabi(q, k, v, m, num_splits=1)
+    assert plan.tile_skip == 1
+    check_against_oracle(out, q, k, v, m[:, :, :, :700].contiguous(), "trap columns")

@@ -27,9 +27,9 @@ def test_library_exports_every_declared_symbol():
 
 
 def test_struct_sizes_match_header_layout():
-    # 2*4 + 6*8 + 8*4 + 2*8 + 4*4 = 120 ; 12*4 + 8 = 56
+    # 2*4 + 6*8 + 8*4 + 2*8 + 4*4 = 120 ; 14*4 + 8 = 64
     assert ctypes.sizeof(_cabi.FaMaskFwdArgs) == 120
-    assert ctypes.sizeof(_cabi.FaMaskFwdPlan) == 56
+    assert ctypes.sizeof(_cabi.FaMaskFwdPlan) == 64
     a = _cabi.make_args(batch=1, heads=1, heads_k=1, seqlen_q=8, seqlen_k=8, head_dim=64,
                         dtype=_cabi.BF16)
     a.struct_size = 64
@@ -49,7 +49,8 @@ def test_plan_of_the_five_configurations():
     sm = _plan().sm_count                      # 148 where no device can be queried
     p = _plan(batch=4, heads=16, heads_k=16, seqlen_q=2048, seqlen_k=2048)
     assert (p.num_splits, p.kv_blocks, p.grid_x, p.q_tiles_per_cta) == (1, 16, 8 * 16 * 4, 2)
-    assert p.workspace_bytes == 0 and p.mask_repitched == 0 and p.threads == 384
+    assert p.tile_skip == 1 and p.workspace_bytes == 512 and p.mask_repitched == 0 and p.threads == 384
+    assert _plan(batch=4, heads=16, heads_k=16, seqlen_q=2048, seqlen_k=2048, no_tile_skip=1).workspace_bytes == 0
     p = _plan(batch=1, heads=16, heads_k=16, seqlen_q=128, seqlen_k=32768)
     assert p.kv_blocks == 256 and p.num_splits == 2 * max(1, sm // 16) and p.q_tiles_per_cta == 1
     assert p.dual_split == 1 and p.grid_x == 16 * ((p.num_splits + 1) // 2)
@@ -60,7 +61,7 @@ def test_plan_of_the_five_configurations():
     assert p.num_splits == 1 and p.kv_blocks == 33 and p.mask_repitched == 1
     assert p.workspace_bytes >= 4 * 1000 * 4104 * 2
     p = _plan(batch=2, heads=4, heads_k=4, seqlen_q=256, seqlen_k=256, head_dim=64)
-    assert p.num_splits == 1 and p.grid_x == 8
+    assert p.num_splits == 1 and p.grid_x == 8 and p.tile_skip == 0
     assert p.smem_bytes <= 232448
 
 
