@@ -302,12 +302,14 @@ def run_ours(args, w):
     starts = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
     ends = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
     barrier()
+    launches_before = _cabi.launch_count()
     for i in range(args.steps):
         flush.zero_()                       # evict L2 between steps (outside the events)
         starts[i].record(stream)
         step_kernel()
         ends[i].record(stream)
     barrier()
+    kernel_launches = _cabi.launch_count() - launches_before
     step_ms = [s.elapsed_time(e) for s, e in zip(starts, ends)]
     mean_ms = sum(step_ms) / len(step_ms)
     med_ms = statistics.median(step_ms)
@@ -362,7 +364,9 @@ def run_ours(args, w):
                                        f"(batch, head) sharded, {world} rank(s), no collective"),
                        "global_batch": w.B if cross_split else w.B * world, "l2": "256 MB zero-fill before every timed step",
                        "timing": "CUDA events per step on the launching stream, mean over steps, max over ranks",
-                       "num_splits": plan.num_splits, "grid": plan.grid_x},
+                       "num_splits": plan.num_splits, "grid": plan.grid_x,
+                       "tile_skip_eligible": bool(plan.tile_skip),
+                       "kernels_per_step_max": launches_per_step},
             "roofline": {"bound": bound, "achieved": achieved, "peak": peak, "unit": unit,
                          "frac": achieved / peak, "traffic": NCU_TRAFFIC_BYTES.get(w.name),
                          "peak_source": f"{peak_src} (MEASURED_PEAKS.json burst figure)"
@@ -372,7 +376,7 @@ def run_ours(args, w):
                     "h2d_bytes_per_step": in_bytes, "d2h_bytes_per_step": out_h.numel() * 2,
                     "ms_per_step": e2e_ms, "wall_ms_per_step": e2e_wall_ms,
                     "api": "custom_ops_b200.ops.mha_fwd_with_mask (torch op recsys_ops::mha_fwd_with_mask)"},
-            "gpu_launches": launches_per_step * args.steps,
+            "gpu_launches": kernel_launches,
             "clocks": clocks,
         }
         if world == 1 and not args.no_cpu_baseline:

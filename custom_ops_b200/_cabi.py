@@ -30,6 +30,7 @@ EXPORTS = [
     "fa_mask_fwd_sm100_static_scratch",
     "fa_mask_fwd_sm100_combine",
     "fa_mask_fwd_sm100_device_status",
+    "fa_mask_fwd_sm100_launch_count",
     "fa_mask_fwd_sm100_strerror",
 ]
 
@@ -124,6 +125,8 @@ def load(path: str | None = None):
     lib.fa_mask_fwd_sm100_device_status.restype = ctypes.c_int
     lib.fa_mask_fwd_sm100_device_status.argtypes = [ctypes.c_int32, P(ctypes.c_uint32),
                                                     ctypes.c_int32]
+    lib.fa_mask_fwd_sm100_launch_count.restype = ctypes.c_int
+    lib.fa_mask_fwd_sm100_launch_count.argtypes = [P(ctypes.c_uint64)]
     lib.fa_mask_fwd_sm100_strerror.restype = ctypes.c_char_p
     lib.fa_mask_fwd_sm100_strerror.argtypes = [ctypes.c_int]
     if lib.fa_mask_fwd_sm100_abi_version() != ABI_VERSION:
@@ -205,3 +208,10 @@ def device_status(device: int = 0, clear: bool = True) -> int:
     if rc not in (0, -10):
         check(rc)
     return int(st.value)
+
+
+def launch_count() -> int:
+    """Kernels launched by the library in this process so far."""
+    n = ctypes.c_uint64(0)
+    check(load().fa_mask_fwd_sm100_launch_count(ctypes.byref(n)))
+    return int(n.value)

@@ -45,6 +45,7 @@
 
 #include <cmath>
 #include <cstdint>
+#include <atomic>
 #include <cstring>
 #include <mutex>
 
@@ -130,7 +131,7 @@ __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
     else return pack_f16x2(lo, hi);
 }
 
-template <int D, bool BF16>
+template <int D, bool BF16, bool LIST>
 __global__ void __launch_bounds__(kThreads, 1)
 fa_mask_fwd_kernel(const __grid_constant__ CUtensorMap tm_q,
                    const __grid_constant__ CUtensorMap tm_k,
@@ -196,7 +197,7 @@ fa_mask_fwd_kernel(const __grid_constant__ CUtensorMap tm_q,
     // is -inf for all 256 rows of this pair.  The idle warp compacts the flags into a list of
     // the blocks to visit; every role then walks the list instead of 0..kv_blocks-1.  Skipping
     // such a block is exact: all of its weights would be 0.
-    const bool use_list = (p.block_flags != nullptr);
+    constexpr bool use_list = LIST;        // compiled twice: with and without the skip list
     if (use_list && warp == 11) {
         pdl_wait_prior_grid();                 // the flags come from the pre-pass kernel
         const unsigned char* fl = p.block_flags +
@@ -825,9 +826,13 @@ fa_mask_combine_kernel(const float* __restrict__ o_parts, const float* __restric
 // reading at the first pass that saw a visible entry, so a mask without all-masked regions
 // costs a few kilobytes per CTA.
 // ---------------------------------------------------------------------------------
+// per-launch tally of skippable regions and a ticket that finds the last CTA
+__device__ unsigned int g_skip_count = 0;
+__device__ unsigned int g_skip_ticket = 0;
+
 __global__ void __launch_bounds__(256)
 fa_mask_classify_kernel(const uint16_t* __restrict__ mask, long long bs, long long rs, int Sq, int Sk,
-                        uint32_t neg_inf2, unsigned char* __restrict__ flags) {
+                        uint32_t neg_inf2, unsigned char* __restrict__ flags, int* hint) {
     const int nt = blockIdx.x, mp = blockIdx.y, b = blockIdx.z;
     pdl_wait_prior_grid();                          // a re-pitch kernel may have written the mask
     pdl_launch_dependents();
@@ -857,8 +862,24 @@ fa_mask_classify_kernel(const uint16_t* __restrict__ mask, long long bs, long lo
             break;
         }
     }
-    if (threadIdx.x == 0)
+    if (threadIdx.x == 0) {
         flags[(static_cast<long long>(b) * gridDim.y + mp) * gridDim.x + nt] = visible ? 1 : 0;
+        // Tell the host whether this mask has regions worth skipping: the CTAs tally on the
+        // device and the last one to finish writes the total, once, to a word of mapped
+        // pinned host memory that the host reads on a later call without synchronising.
+        // (Only a heuristic input: overlapping launches may blur the tally, never a result.)
+        if (hint != nullptr) {
+            if (!visible) atomicAdd(&g_skip_count, 1u);
+            __threadfence();
+            const unsigned int total = gridDim.x * gridDim.y * gridDim.z;
+            if (atomicAdd(&g_skip_ticket, 1u) == total - 1) {
+                *reinterpret_cast<volatile int*>(hint) =
+                    static_cast<int>(*reinterpret_cast<volatile unsigned int*>(&g_skip_count)) + 1;
+                g_skip_count = 0;
+                g_skip_ticket = 0;
+            }
+        }
+    }
 }
 
 // ---------------------------------------------------------------------------------
@@ -883,11 +904,14 @@ fa_mask_repitch_kernel(const uint16_t* __restrict__ src, uint16_t* __restrict__ 
 // ---------------------------------------------------------------------------------
 constexpr int kMaxDevices = 64;
 
+// Kernels launched by this library since it was loaded (for benchmarks that must count them).
+static std::atomic<unsigned long long> g_launches{0};
+
 struct DeviceInfo {
     int sm_count = 0;
     int cc_major = 0;
     unsigned int* status_ptr = nullptr;
-    bool attr_set[4] = {false, false, false, false};
+    bool attr_set[8] = {false, false, false, false, false, false, false, false};
     bool queried = false;
 };
 static DeviceInfo g_dev[kMaxDevices];
@@ -1115,11 +1139,11 @@ static int get_maps(const MapKey& key, CUtensorMap* tq, CUtensorMap* tk, CUtenso
     return FA_SM100_OK;
 }
 
-template <int D, bool BF16>
+template <int D, bool BF16, bool LIST>
 static int launch_fwd(DeviceInfo* dev, int slot, const CUtensorMap& tq, const CUtensorMap& tk,
                       const CUtensorMap& tv, const CUtensorMap& tm, const KParams& kp, dim3 grid,
                       cudaStream_t stream, bool chained) {
-    auto kern = fa_mask_fwd_kernel<D, BF16>;
+    auto kern = fa_mask_fwd_kernel<D, BF16, LIST>;
     if (!dev->attr_set[slot]) {
         // The in-kernel register re-balancing is only sound for the register count it was
         // written for; refuse to launch a build that came out different.
@@ -1151,10 +1175,12 @@ static int launch_fwd(DeviceInfo* dev, int slot, const CUtensorMap& tq, const CU
             cudaGetLastError();
             return FA_SM100_ERR_CUDA;
         }
+        ++g_launches;
         return FA_SM100_OK;
     }
     kern<<<grid, kThreads, Cfg<D>::kSmemBytes, stream>>>(tq, tk, tv, tm, kp);
     if (cudaGetLastError() != cudaSuccess) return FA_SM100_ERR_CUDA;
+    ++g_launches;
     return FA_SM100_OK;
 }
 
@@ -1188,6 +1214,7 @@ static int launch_combine(const float* o_parts, const float* lse_parts, void* ou
             cudaGetLastError();
             return FA_SM100_ERR_CUDA;
         }
+        ++g_launches;
         return FA_SM100_OK;
     }
     if (d == 128)
@@ -1196,7 +1223,9 @@ static int launch_combine(const float* o_parts, const float* lse_parts, void* ou
     else
         fa_mask_combine_kernel<64><<<blocks, warps * 32, 0, stream>>>(
             o_parts, lse_parts, out, lse_out, parts, rows, dtype == FA_SM100_BF16, out_fp32);
-    return cudaGetLastError() == cudaSuccess ? FA_SM100_OK : FA_SM100_ERR_CUDA;
+    if (cudaGetLastError() != cudaSuccess) return FA_SM100_ERR_CUDA;
+    ++g_launches;
+    return FA_SM100_OK;
 }
 
 static int status_pointer(DeviceInfo* dev) {
@@ -1211,8 +1240,96 @@ static int status_pointer(DeviceInfo* dev) {
     return FA_SM100_OK;
 }
 
+// ---------------------------------------------------------------------------------
+// Is the tile-skip pre-pass worth running for this mask?
+// ---------------------------------------------------------------------------------
+// The pre-pass costs a few microseconds and gates the attention kernel.  For a mask without
+// any fully masked 256 x 128 region (an unstructured random mask) it buys nothing, so the
+// launcher remembers, per mask buffer and shape, what the last pre-pass found: the pre-pass
+// kernel counts the skippable regions into a word of mapped pinned host memory, which the
+// host reads on a LATER call without synchronising anything.  Two pre-passes in a row that
+// found nothing switch it off for the next kSkipHoldoff calls with that mask; then it is
+// tried again.  Only whether the optimisation runs depends on this; results never do.
+constexpr int kHintSlots = 16;
+constexpr int kSkipHoldoff = 30;
+struct SkipHint {
+    const void* mask = nullptr;
+    long long bs = 0, rs = 0;
+    int B = 0, Sq = 0, Sk = 0, dtype = 0, device = 0;
+    int zero_streak = 0;
+    int holdoff = 0;
+    bool ran_last = false;
+    bool valid = false;
+};
+static SkipHint g_hints[kHintSlots];
+static int g_hint_next = 0;
+static int* g_hint_words = nullptr;          // kHintSlots ints, pinned + mapped
+static bool g_hint_failed = false;
+static std::mutex g_hint_mutex;
+
+// Returns true when the pre-pass should run; *counter is where it should count (or NULL).
+static bool want_classify(const FaMaskFwdArgs* a, const void* mask, long long bs, long long rs,
+                          bool adaptive, int** counter) {
+    *counter = nullptr;
+    if (!adaptive) return true;
+    std::lock_guard<std::mutex> lock(g_hint_mutex);
+    if (g_hint_words == nullptr && !g_hint_failed) {
+        void* ptr = nullptr;
+        if (cudaHostAlloc(&ptr, kHintSlots * sizeof(int), cudaHostAllocMapped | cudaHostAllocPortable) !=
+            cudaSuccess) {
+            cudaGetLastError();
+            g_hint_failed = true;
+        } else {
+            g_hint_words = static_cast<int*>(ptr);
+            std::memset(g_hint_words, 0, kHintSlots * sizeof(int));
+        }
+    }
+    if (g_hint_words == nullptr) return true;
+    int slot = -1;
+    for (int i = 0; i < kHintSlots; ++i) {
+        const SkipHint& h = g_hints[i];
+        if (h.valid && h.mask == mask && h.bs == bs && h.rs == rs && h.B == a->batch &&
+            h.Sq == a->seqlen_q && h.Sk == a->seqlen_k && h.dtype == a->dtype && h.device == a->device) {
+            slot = i;
+            break;
+        }
+    }
+    if (slot < 0) {
+        slot = g_hint_next;
+        g_hint_next = (g_hint_next + 1) % kHintSlots;
+        SkipHint fresh;
+        fresh.mask = mask; fresh.bs = bs; fresh.rs = rs; fresh.B = a->batch; fresh.Sq = a->seqlen_q;
+        fresh.Sk = a->seqlen_k; fresh.dtype = a->dtype; fresh.device = a->device; fresh.valid = true;
+        g_hints[slot] = fresh;
+    }
+    SkipHint& h = g_hints[slot];
+    volatile int* word = g_hint_words + slot;
+    if (h.holdoff > 0) {
+        --h.holdoff;
+        h.ran_last = false;
+        return false;
+    }
+    if (h.ran_last) {
+        // 0: the last pre-pass has not reported yet; 1: it found nothing to skip; > 1: it did
+        if (*word == 1) {
+            if (++h.zero_streak >= 2) {
+                h.zero_streak = 0;
+                h.holdoff = kSkipHoldoff;
+                h.ran_last = false;
+                return false;
+            }
+        } else if (*word > 1) {
+            h.zero_streak = 0;
+        }
+    }
+    *word = 0;
+    h.ran_last = true;
+    *counter = g_hint_words + slot;            // unified addressing: same pointer on the device
+    return true;
+}
+
 static int forward(const FaMaskFwdArgs* a, void* workspace, size_t workspace_bytes,
-                   cudaStream_t stream) {
+                   cudaStream_t stream, bool adaptive_skip = true) {
     FaMaskFwdPlan plan;
     int rc = make_plan(a, &plan);
     if (rc != FA_SM100_OK) return rc;
@@ -1273,11 +1390,15 @@ static int forward(const FaMaskFwdArgs* a, void* workspace, size_t workspace_byt
         fa_mask_repitch_kernel<<<blocks, 256, 0, stream>>>(
             mask_ptr, dst, a->seqlen_q, a->seqlen_k, pitch, mask_bs, mask_rs);
         if (cudaGetLastError() != cudaSuccess) return FA_SM100_ERR_CUDA;
+        ++g_launches;
         mask_ptr = dst;
         mask_bs = static_cast<long long>(a->seqlen_q) * pitch;
         mask_rs = pitch;
     }
-    if (plan.tile_skip) {
+    int* hint_counter = nullptr;
+    const bool run_classify = plan.tile_skip &&
+        want_classify(a, mask_ptr, mask_bs, mask_rs, adaptive_skip, &hint_counter);
+    if (run_classify) {
         unsigned char* flags = ws + (plan.mask_repitched
             ? align256(static_cast<size_t>(a->batch) * a->seqlen_q * ((a->seqlen_k + 7) & ~7) * 2) : 0);
         const dim3 cgrid(plan.kv_blocks, ceil_div(a->seqlen_q, 2 * kBlockM), a->batch);
@@ -1292,10 +1413,11 @@ static int forward(const FaMaskFwdArgs* a, void* workspace, size_t workspace_byt
         cfg.attrs = attr;
         cfg.numAttrs = plan.mask_repitched ? 1 : 0;      // chained behind the re-pitch kernel
         if (cudaLaunchKernelEx(&cfg, fa_mask_classify_kernel, mask_ptr, mask_bs, mask_rs, a->seqlen_q,
-                               a->seqlen_k, ninf, flags) != cudaSuccess) {
+                               a->seqlen_k, ninf, flags, hint_counter) != cudaSuccess) {
             cudaGetLastError();
             return FA_SM100_ERR_CUDA;
         }
+        ++g_launches;
         kp.block_flags = flags;
     }
     kp.out = a->out;
@@ -1322,14 +1444,20 @@ static int forward(const FaMaskFwdArgs* a, void* workspace, size_t workspace_byt
     if ((rc = get_maps(key, &tq, &tk, &tv, &tm)) != FA_SM100_OK) return rc;
 
     const dim3 grid(plan.grid_x, plan.grid_y, plan.grid_z);
-    const bool chained = plan.mask_repitched || plan.tile_skip;
+    const bool chained = plan.mask_repitched || run_classify;
     const bool bf16 = a->dtype == FA_SM100_BF16;
+    const bool list = kp.block_flags != nullptr;
+    const int slot = (d == 128 ? 0 : 2) + (bf16 ? 0 : 1) + (list ? 4 : 0);
     if (d == 128) {
-        rc = bf16 ? launch_fwd<128, true>(dev, 0, tq, tk, tv, tm, kp, grid, stream, chained)
-                  : launch_fwd<128, false>(dev, 1, tq, tk, tv, tm, kp, grid, stream, chained);
+        if (list) rc = bf16 ? launch_fwd<128, true, true>(dev, slot, tq, tk, tv, tm, kp, grid, stream, chained)
+                            : launch_fwd<128, false, true>(dev, slot, tq, tk, tv, tm, kp, grid, stream, chained);
+        else rc = bf16 ? launch_fwd<128, true, false>(dev, slot, tq, tk, tv, tm, kp, grid, stream, chained)
+                       : launch_fwd<128, false, false>(dev, slot, tq, tk, tv, tm, kp, grid, stream, chained);
     } else {
-        rc = bf16 ? launch_fwd<64, true>(dev, 2, tq, tk, tv, tm, kp, grid, stream, chained)
-                  : launch_fwd<64, false>(dev, 3, tq, tk, tv, tm, kp, grid, stream, chained);
+        if (list) rc = bf16 ? launch_fwd<64, true, true>(dev, slot, tq, tk, tv, tm, kp, grid, stream, chained)
+                            : launch_fwd<64, false, true>(dev, slot, tq, tk, tv, tm, kp, grid, stream, chained);
+        else rc = bf16 ? launch_fwd<64, true, false>(dev, slot, tq, tk, tv, tm, kp, grid, stream, chained)
+                       : launch_fwd<64, false, false>(dev, slot, tq, tk, tv, tm, kp, grid, stream, chained);
     }
     if (rc != FA_SM100_OK) return rc;
     if (plan.num_splits > 1)
@@ -1374,7 +1502,8 @@ static int forward_static_scratch(const FaMaskFwdArgs* a, cudaStream_t stream) {
             scratch = ptr;
         }
     }
-    return forward(a, scratch, FA_SM100_STATIC_SCRATCH_BYTES, stream);
+    // (no adaptive pre-pass gating here: that would allocate a pinned host word)
+    return forward(a, scratch, FA_SM100_STATIC_SCRATCH_BYTES, stream, /*adaptive_skip=*/false);
 }
 
 }  // namespace fa_sm100
@@ -1453,6 +1582,12 @@ int fa_mask_fwd_sm100_device_status(int32_t device, uint32_t* status, int32_t cl
 
 int fa_mask_fwd_sm100_static_scratch(const FaMaskFwdArgs* args, void* stream) {
     return fa_sm100::forward_static_scratch(args, static_cast<cudaStream_t>(stream));
+}
+
+int fa_mask_fwd_sm100_launch_count(uint64_t* launches) {
+    if (launches == nullptr) return FA_SM100_ERR_NULL;
+    *launches = fa_sm100::g_launches.load();
+    return FA_SM100_OK;
 }
 
 const char* fa_mask_fwd_sm100_strerror(int code) {

@@ -10,7 +10,8 @@
  * FA_SM100_ERR_* code, never throws, never synchronises the device (except
  * fa_mask_fwd_sm100_device_status, which says so) and never allocates device
  * memory: outputs and the workspace belong to the caller.  Work is enqueued on
- * the caller's stream.
+ * the caller's stream.  (fa_mask_fwd_sm100 keeps 64 bytes of pinned HOST memory, allocated
+ * on first use, for the tile-skip heuristic described at FaMaskFwdPlan.tile_skip.)
  */
 #ifndef FA_MASK_FWD_SM100_H_
 #define FA_MASK_FWD_SM100_H_
@@ -98,7 +99,11 @@ typedef struct FaMaskFwdPlan {
     int32_t mask_repitched;     /* 1 when the mask is first copied to an aligned pitch */
     int32_t sm_count;
     int32_t dual_split;         /* 1: one query tile per CTA, two KV splits side by side */
-    int32_t tile_skip;          /* 1: a pre-pass finds key blocks masked for a whole 256-row pair; they are skipped */
+    int32_t tile_skip;          /* 1: eligible for tile skipping: a pre-pass kernel finds the key blocks
+                                 * whose mask is -inf for a whole 256-row query pair and the attention
+                                 * kernel does not visit them (exact: their weights are 0).  The
+                                 * launcher drops the pre-pass for a while after it found nothing to
+                                 * skip twice in a row for the same mask buffer and shape. */
     int32_t reserved;
     uint64_t workspace_bytes;
 } FaMaskFwdPlan;
@@ -162,6 +167,11 @@ int fa_mask_fwd_sm100_combine(const float* o_parts, const float* lse_parts, void
  * word: 0, or the code of the first bounded wait that ran out.  Clears it when
  * `clear` != 0.  No counterpart in the reference, whose kernels wait unbounded. */
 int fa_mask_fwd_sm100_device_status(int32_t device, uint32_t* status, int32_t clear);
+
+/* Number of GPU kernels this library has launched in this process so far (attention, merge,
+ * mask re-pitch and tile-skip pre-pass kernels).  For benchmarks that must report how many of
+ * the library's kernels ran in a timed region.  No counterpart in the reference. */
+int fa_mask_fwd_sm100_launch_count(uint64_t* launches);
 
 /* Text for a return code.  Stands in for the TORCH_CHECK messages of
  * csrc/fa/fa_fwd_op.cu:53-108 and csrc/fa/fa_fwd_launch.h:596-602. */
