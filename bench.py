@@ -49,8 +49,8 @@ FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustain
 # dram__bytes_read.sum + dram__bytes_write.sum of one attention-kernel launch, from
 # the ncu captures summarised under profiles/ (None until a capture exists).
 NCU_TRAFFIC_BYTES = {
-    "standard": 154.9e6,        # profiles/fa_mask_fwd_kernel_standard.md (135.2 MB read + 19.7 MB written)
-    "splitkv_long": 285.2e6,    # profiles/fa_mask_fwd_kernel_splitkv_long.md (277.95 MB + 7.27 MB)
+    "standard": 154.9e6,        # 135.2 MB read + 19.7 MB written (ncu summary of the standard workload)
+    "splitkv_long": 285.2e6,    # 277.95 MB read + 7.27 MB written (ncu summary of the long-context workload)
 }
 
 

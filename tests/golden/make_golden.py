@@ -5,7 +5,7 @@ outputs of the REFERENCE's own test oracle ``ref_attn``
 
 Run where the reference checkout is mounted:
 
-    python tests/golden/make_golden.py [--reference /root/reference]
+    python tests/golden/make_golden.py --reference <path to the reference checkout>
 
 The reference's root directory *is* the package ``custom_ops``; its test module
 does ``from custom_ops import ops`` at import time (lazy, nothing is compiled),
@@ -88,7 +88,7 @@ def make_case(gen, dtype, B, H, Hk, Sq, Sk, d, kind, pad_rows, pad_cols):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", default=os.environ.get("CUSTOM_OPS_REFERENCE", "/root/reference"))
     ap.add_argument("--out", default=os.path.join(os.path.dirname(os.path.abspath(__file__)),
                                                   "ref_attn_cases.npz"))
     args = ap.parse_args()
