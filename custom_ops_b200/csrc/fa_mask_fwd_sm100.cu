@@ -93,7 +93,7 @@ struct Cfg {
     static constexpr uint32_t kSubBytes = kPanelBytes;            // 64-column swizzle panel
     static constexpr int kSub = D / 64;
     static constexpr uint32_t kMaskBytes = 4 * kPanelBytes;       // 2 tiles x 2 panels
-    static constexpr uint32_t kBarBytes = 256;
+    static constexpr uint32_t kBarBytes = 320;
     static constexpr uint32_t kListBytes = kMaxListBlocks * 2;   // compacted key-block list (uint16)
     static constexpr uint32_t kSmemBytes =
         1024 + 2 * kTileBytes + kStages * kTileBytes + kMaskBytes + kBarBytes + kListBytes;
@@ -152,7 +152,8 @@ fa_mask_fwd_kernel(const __grid_constant__ CUtensorMap tm_q,
     const uint32_t sBar = sM + C::kMaskBytes;
     const uint32_t bar_q_full = sBar;                  // [2]
     const uint32_t bar_s_full = sBar + 16;             // [2]
-    const uint32_t bar_p_ready = sBar + 32;            // [2]
+    const uint32_t bar_p_ready = sBar + 32;            // [2] first 64 keys of P written
+    const uint32_t bar_p_ready2 = sBar + 256;          // [2] last 64 keys of P written
     const uint32_t bar_o_full = sBar + 48;             // [2]
     const uint32_t bar_m_full = sBar + 64;             // [4]
     const uint32_t bar_m_empty = sBar + 96;            // [4]
@@ -218,6 +219,7 @@ fa_mask_fwd_kernel(const __grid_constant__ CUtensorMap tm_q,
             mbar_init(bar_q_full + 8 * t, 1);
             mbar_init(bar_s_full + 8 * t, 1);
             mbar_init(bar_p_ready + 8 * t, kSoftmaxThreads);
+            mbar_init(bar_p_ready2 + 8 * t, kSoftmaxThreads);
             mbar_init(bar_o_full + 8 * t, 1);
         }
         for (int i = 0; i < 4; ++i) {
@@ -397,13 +399,27 @@ fa_mask_fwd_kernel(const __grid_constant__ CUtensorMap tm_q,
                 };
                 // O_t += P_t V : A = P in tensor memory (two 16-bit values per column),
                 // B = V tile, d contiguous (MN-major), 16 keys per step.
-                auto issue_pv = [&](int t, uint32_t v_addr, bool acc) {
+                // P arrives in two halves of 64 keys: the first half's MMAs run while the
+                // softmax threads are still producing the second.
+                auto issue_pv_half = [&](int t, uint32_t v_addr, bool acc, int half) {
 #pragma unroll
-                    for (int ks = 0; ks < kBlockN / 16; ++ks) {
+                    for (int kk = 0; kk < kBlockN / 32; ++kk) {
+                        const int ks = half * (kBlockN / 32) + kk;
                         const uint64_t db = smem_desc_sw128(v_addr + ks * 2048, SUB, 1024);
                         mma_ts(tO0 + t * 128, tS0 + t * 128 + ks * 8, db, idesc_o,
                                (acc || ks > 0) ? 1u : 0u);
                     }
+                };
+
+                // waits for the two halves of P of step j in turn and issues their MMAs
+                auto issue_pv = [&](int t, uint32_t v_addr, int j) -> bool {
+                    if (!mbar_wait(bar_p_ready + 8 * t, j & 1, abort_flag, p.status, kStMmaP)) return false;
+                    tc_fence_after();
+                    issue_pv_half(t, v_addr, j > 0, 0);
+                    if (!mbar_wait(bar_p_ready2 + 8 * t, j & 1, abort_flag, p.status, kStMmaP)) return false;
+                    tc_fence_after();
+                    issue_pv_half(t, v_addr, true, 1);
+                    return true;
                 };
 
                 bool ok = (n > 0) && mbar_wait(bar_q_full, 0, abort_flag, p.status, kStMmaQ);
@@ -438,11 +454,7 @@ fa_mask_fwd_kernel(const __grid_constant__ CUtensorMap tm_q,
                         for (int t = 0; t < 2; ++t) {
                             if (!ok || j >= sl_n[t]) continue;
                             if (!(ok = take(addr))) break;                       // V_t(j)
-                            if (!(ok = mbar_wait(bar_p_ready + 8 * t, j & 1, abort_flag, p.status,
-                                                 kStMmaP)))
-                                break;
-                            tc_fence_after();
-                            issue_pv(t, addr, j > 0);
+                            if (!(ok = issue_pv(t, addr, j))) break;
                             release();
                             if (j + 1 < sl_n[t]) {
                                 if (!(ok = take(addr))) break;                   // K_t(j+1)
@@ -482,9 +494,7 @@ fa_mask_fwd_kernel(const __grid_constant__ CUtensorMap tm_q,
                                          p.status, kStMmaKv)))
                         break;
                     // ---- tile 0
-                    if (!(ok = mbar_wait(bar_p_ready, j & 1, abort_flag, p.status, kStMmaP))) break;
-                    tc_fence_after();
-                    issue_pv(0, v_addr, j > 0);
+                    if (!(ok = issue_pv(0, v_addr, j))) break;
                     if (more) {
                         if (!(ok = mbar_wait(bar_kv_full + 8 * (fk % NS), (fk / NS) & 1, abort_flag,
                                              p.status, kStMmaKv)))
@@ -497,10 +507,7 @@ fa_mask_fwd_kernel(const __grid_constant__ CUtensorMap tm_q,
                     }
                     // ---- tile 1
                     if (has_q1) {
-                        if (!(ok = mbar_wait(bar_p_ready + 8, j & 1, abort_flag, p.status, kStMmaP)))
-                            break;
-                        tc_fence_after();
-                        issue_pv(1, v_addr, j > 0);
+                        if (!(ok = issue_pv(1, v_addr, j))) break;
                         mma_commit(bar_kv_empty + 8 * (fv % NS));
                         if (more) {
                             issue_s(1, k_addr);
@@ -532,6 +539,7 @@ fa_mask_fwd_kernel(const __grid_constant__ CUtensorMap tm_q,
             const uint32_t tO = tmem_base + lane_sel + 256 + t * 128;
             const uint32_t bar_s = bar_s_full + 8 * t;
             const uint32_t bar_p = bar_p_ready + 8 * t;
+            const uint32_t bar_p2 = bar_p_ready2 + 8 * t;
             // this thread's row inside a swizzled mask panel: 16-byte chunk c of row r
             // lives at r*128 + ((c ^ (r & 7)) << 4)
             const uint32_t m_row_addr = sM + (2 * t) * kPanelBytes + row_in_tile * 128;
@@ -639,11 +647,17 @@ fa_mask_fwd_kernel(const __grid_constant__ CUtensorMap tm_q,
                         pk[i + 1] = pack2<BF16>(p1.x, p1.y);
                     }
                     tmem_st16(tS + c * 16, pk);
+                    if (c == 1) {
+                        // first 64 keys of P are in tensor memory: their MMAs may start
+                        tmem_wait_st();
+                        tc_fence_before();
+                        mbar_arrive(bar_p);
+                    }
                 }
                 l = l * alpha + ((sum_a.x + sum_a.y) + (sum_b.x + sum_b.y));
                 tmem_wait_st();
                 tc_fence_before();
-                mbar_arrive(bar_p);
+                mbar_arrive(bar_p2);
             }
 
             // ---- epilogue: O / l, to the output dtype (or fp32 partial + LSE when split)
