@@ -337,6 +337,27 @@ __device__ __forceinline__ float lg2(float x) {
     return y;
 }
 
+// 2^t for two values on the FMA pipes instead of the special-function unit: round t to an
+// integer n with the 1.5*2^23 trick, evaluate a cubic for 2^(t-n) on [-0.5, 0.5] (relative
+// error 7.5e-5, far below the 16-bit rounding of P) and add n to the exponent field.
+// t is clamped at -126, so -inf gives about 1e-38 rather than 0; callers must not rely on an
+// exact zero (the kernel decides "fully masked row" from the running maximum instead).
+__device__ __forceinline__ float2 ex2_poly2(float2 t) {
+    t.x = fmaxf(t.x, -126.f);
+    t.y = fmaxf(t.y, -126.f);
+    const float2 magic = make_float2(12582912.f, 12582912.f);
+    const float2 tt = __fadd2_rn(t, magic);                               // low mantissa bits = n
+    const float2 n = __fadd2_rn(tt, make_float2(-12582912.f, -12582912.f));
+    const float2 fr = __ffma2_rn(n, make_float2(-1.f, -1.f), t);          // t - n
+    float2 p = __ffma2_rn(fr, make_float2(0.055171649903059006f, 0.055171649903059006f),
+                          make_float2(0.2426111251115799f, 0.2426111251115799f));
+    p = __ffma2_rn(p, fr, make_float2(0.6932609677314758f, 0.6932609677314758f));
+    p = __ffma2_rn(p, fr, make_float2(0.9999280571937561f, 0.9999280571937561f));
+    p.x = __int_as_float(__float_as_int(p.x) + (__float_as_int(tt.x) << 23));
+    p.y = __int_as_float(__float_as_int(p.y) + (__float_as_int(tt.y) << 23));
+    return p;
+}
+
 __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
     uint32_t r;
     asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
