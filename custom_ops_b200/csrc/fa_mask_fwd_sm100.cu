@@ -154,6 +154,7 @@ fa_mask_fwd_kernel(const __grid_constant__ CUtensorMap tm_q,
     const uint32_t bar_s_full = sBar + 16;             // [2]
     const uint32_t bar_p_ready = sBar + 32;            // [2] first 64 keys of P written
     const uint32_t bar_p_ready2 = sBar + 256;          // [2] last 64 keys of P written
+    const uint32_t bar_merge = sBar + 272;             // dual mode: both slots have their final O
     const uint32_t bar_o_full = sBar + 48;             // [2]
     const uint32_t bar_m_full = sBar + 64;             // [4]
     const uint32_t bar_m_empty = sBar + 96;            // [4]
@@ -230,6 +231,7 @@ fa_mask_fwd_kernel(const __grid_constant__ CUtensorMap tm_q,
             mbar_init(bar_kv_full + 8 * i, 1);
             mbar_init(bar_kv_empty + 8 * i, 1);
         }
+        mbar_init(bar_merge, 2 * kSoftmaxThreads);
         *abort_flag = 0;
         fence_barrier_init();
         prefetch_tensormap(&tm_q);
@@ -671,7 +673,59 @@ fa_mask_fwd_kernel(const __grid_constant__ CUtensorMap tm_q,
                 bool ok = mbar_wait(bar_o_full + 8 * t, 0, abort_flag, p.status, kStSoftmaxO);
                 alive = __all_sync(0xffffffffu, ok);
             }
-            if (alive) {
+            const bool merge_slots = dual && sl_n[0] > 0 && sl_n[1] > 0;
+            if (alive && merge_slots) {
+                // Dual mode: the two slots hold partial results of the SAME rows over two key
+                // ranges.  They are merged here, in the CTA, so one partial goes to memory
+                // instead of two: each group publishes (max, sum) of its rows in its own, now
+                // idle, mask panel, reads the other group's, and normalises half of the
+                // columns of  a0*O0 + a1*O1  straight out of tensor memory.
+                const uint32_t own = sM + (2 * t) * kPanelBytes + row_in_tile * 8;
+                const uint32_t other = sM + (2 * (t ^ 1)) * kPanelBytes + row_in_tile * 8;
+                sts32(own, __float_as_uint(m_ref));
+                sts32(own + 4, __float_as_uint(l));
+                mbar_arrive(bar_merge);
+                bool ok = mbar_wait(bar_merge, 0, abort_flag, p.status, kStSoftmaxO);
+                alive = __all_sync(0xffffffffu, ok);
+                if (alive) {
+                    tc_fence_after();
+                    const float m_o = __uint_as_float(lds32(other));
+                    const float l_o = __uint_as_float(lds32(other + 4));
+                    const bool dead_s = (m_ref == -INFINITY) || !(l > 0.f);
+                    const bool dead_o = (m_o == -INFINITY) || !(l_o > 0.f);
+                    const float m_all = fmaxf(dead_s ? -INFINITY : m_ref, dead_o ? -INFINITY : m_o);
+                    const float a_s = dead_s ? 0.f : __expf(m_ref - m_all);
+                    const float a_o = dead_o ? 0.f : __expf(m_o - m_all);
+                    const float l_all = a_s * l + a_o * l_o;
+                    const bool dead = dead_s && dead_o;
+                    const float inv = dead ? 0.f : 1.f / l_all;
+                    const float w_s = a_s * inv, w_o = a_o * inv;
+                    const long long prow =
+                        ((static_cast<long long>(sgroup) * p.B + b) * p.H + h) * p.Sq + row;
+                    if (row_ok && t == 0) p.lse_part[prow] = dead ? -INFINITY : m_all + __logf(l_all);
+                    float* dst = p.o_part + prow * D;
+                    const uint32_t tO_other = tmem_base + lane_sel + 256 + (t ^ 1) * 128;
+                    constexpr int kChunks = D / 32;
+#pragma unroll
+                    for (int cc = 0; cc < kChunks / 2; ++cc) {
+                        const int c = t * (kChunks / 2) + cc;          // this group's half of the columns
+                        uint32_t os[32], oo[32];
+                        tmem_ld32(tO + c * 32, os);
+                        tmem_ld32(tO_other + c * 32, oo);
+                        if (row_ok) {
+#pragma unroll
+                            for (int i = 0; i < 32; i += 4) {
+                                float4 f;
+                                f.x = __uint_as_float(os[i]) * w_s + __uint_as_float(oo[i]) * w_o;
+                                f.y = __uint_as_float(os[i + 1]) * w_s + __uint_as_float(oo[i + 1]) * w_o;
+                                f.z = __uint_as_float(os[i + 2]) * w_s + __uint_as_float(oo[i + 2]) * w_o;
+                                f.w = __uint_as_float(os[i + 3]) * w_s + __uint_as_float(oo[i + 3]) * w_o;
+                                *reinterpret_cast<float4*>(dst + c * 32 + i) = f;
+                            }
+                        }
+                    }
+                }
+            } else if (alive) {
                 tc_fence_after();
                 // A row that never saw a visible key still has the reference maximum -inf; its
                 // sum and accumulator hold only rounding dust of the polynomial exponential.
@@ -682,8 +736,9 @@ fa_mask_fwd_kernel(const __grid_constant__ CUtensorMap tm_q,
                 const bool split_out = p.num_splits > 1;
                 float* o32 = nullptr;
                 if (split_out) {
+                    // dual mode stores one partial per CTA (split group), otherwise one per split
                     const long long prow =
-                        ((static_cast<long long>(split) * p.B + b) * p.H + h) * p.Sq + row;
+                        ((static_cast<long long>(dual ? sgroup : split) * p.B + b) * p.H + h) * p.Sq + row;
                     o32 = p.o_part + prow * D;
                     if (row_ok) p.lse_part[prow] = lse_val;
                 } else {
@@ -1064,8 +1119,9 @@ static int make_plan(const FaMaskFwdArgs* a, FaMaskFwdPlan* plan) {
     size_t ws = 0;
     const size_t rows = static_cast<size_t>(a->batch) * a->heads * a->seqlen_q;
     if (splits > 1) {
-        ws += align256(static_cast<size_t>(splits) * rows * d * sizeof(float));
-        ws += align256(static_cast<size_t>(splits) * rows * sizeof(float));
+        // dual mode merges its two splits inside the CTA: one partial per split group
+        ws += align256(static_cast<size_t>(split_groups) * rows * d * sizeof(float));
+        ws += align256(static_cast<size_t>(split_groups) * rows * sizeof(float));
     }
     if (plan->mask_repitched) {
         const size_t pitch = (a->seqlen_k + 7) & ~7;
@@ -1391,10 +1447,11 @@ static int forward(const FaMaskFwdArgs* a, void* workspace, size_t workspace_byt
     float* o_part = nullptr;
     float* lse_part = nullptr;
     if (plan.num_splits > 1) {
+        const int parts = plan.dual_split ? ceil_div(plan.num_splits, 2) : plan.num_splits;
         o_part = reinterpret_cast<float*>(ws);
-        ws += align256(static_cast<size_t>(plan.num_splits) * rows * d * sizeof(float));
+        ws += align256(static_cast<size_t>(parts) * rows * d * sizeof(float));
         lse_part = reinterpret_cast<float*>(ws);
-        ws += align256(static_cast<size_t>(plan.num_splits) * rows * sizeof(float));
+        ws += align256(static_cast<size_t>(parts) * rows * sizeof(float));
     }
     KParams kp;
     std::memset(&kp, 0, sizeof(kp));
@@ -1481,8 +1538,9 @@ static int forward(const FaMaskFwdArgs* a, void* workspace, size_t workspace_byt
     }
     if (rc != FA_SM100_OK) return rc;
     if (plan.num_splits > 1)
-        rc = launch_combine(o_part, lse_part, a->out, a->lse, plan.num_splits, rows, d, a->dtype,
-                            a->out_fp32, stream, /*chained=*/true);
+        rc = launch_combine(o_part, lse_part, a->out, a->lse,
+                            plan.dual_split ? ceil_div(plan.num_splits, 2) : plan.num_splits, rows, d,
+                            a->dtype, a->out_fp32, stream, /*chained=*/true);
     return rc;
 }
 
