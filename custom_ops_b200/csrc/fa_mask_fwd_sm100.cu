@@ -45,6 +45,8 @@
 
 #include <cmath>
 #include <cstdint>
+#include <cstdio>
+#include <cstdlib>
 #include <atomic>
 #include <cstring>
 #include <mutex>
@@ -68,10 +70,15 @@ constexpr int kThreads = 384;
 // blocks until that is there, so the books must balance or the softmax warps wait forever.
 constexpr int kLaunchRegs = 168;
 constexpr int kSoftmaxRegs = 224;
-constexpr int kOtherRegs = 56;
+constexpr int kOtherRegs = 56;        // warps 8-11: one warpgroup, which must ask for one common count
 static_assert(8 * (kSoftmaxRegs - kLaunchRegs) <= 4 * (kLaunchRegs - kOtherRegs),
               "setmaxnreg.inc would ask for more registers than setmaxnreg.dec releases");
 static_assert(kThreads * kLaunchRegs <= 65536, "launch register budget");
+// The register file is split between the four schedulers of an SM, and warp w lives on
+// scheduler w % 4: each scheduler holds two softmax warps and one helper warp, and its
+// quarter of the file (512 registers per lane) must hold all three after the re-balancing.
+static_assert(2 * kSoftmaxRegs + kOtherRegs <= 512,
+              "a scheduler's quarter of the register file cannot hold its three warps");
 constexpr uint32_t kTmemCols = 512;
 constexpr int kMaxListBlocks = 512;    // key blocks a CTA can keep a skip list for (Sk <= 65536)
 constexpr float kLog2e = 1.4426950408889634f;
@@ -97,6 +104,7 @@ struct Cfg {
     static constexpr uint32_t kListBytes = kMaxListBlocks * 2;   // compacted key-block list (uint16)
     static constexpr uint32_t kSmemBytes =
         1024 + 2 * kTileBytes + kStages * kTileBytes + kMaskBytes + kBarBytes + kListBytes;
+    static_assert(kSmemBytes <= 227 * 1024, "more shared memory than a CTA can have");
 };
 
 struct KParams {
@@ -390,13 +398,17 @@ fa_mask_fwd_kernel(const __grid_constant__ CUtensorMap tm_q,
 
                 // S_t = Q_t K^T : A and B both K-major, 64-column 128B-swizzled panels.
                 auto issue_s = [&](int t, uint32_t k_addr) {
-                    const uint32_t q_addr = dual ? sQ : sQ + t * TILE;   // dual: both slots share Q
+                    uint32_t q_addr = dual ? sQ : sQ + t * TILE;   // dual: both slots share Q
+                    // Built afresh at every call: left to itself the compiler keeps all of the
+                    // loop-invariant Q descriptors in registers this warp does not have.
+                    asm volatile("" : "+r"(q_addr));
+                    const uint64_t da0 = smem_desc_sw128(q_addr, 16, 1024);
+                    const uint64_t db0 = smem_desc_sw128(k_addr, 16, 1024);
 #pragma unroll
                     for (int ks = 0; ks < D / 16; ++ks) {
-                        const uint32_t off = (ks >> 2) * SUB + (ks & 3) * 32;
-                        const uint64_t da = smem_desc_sw128(q_addr + off, 16, 1024);
-                        const uint64_t db = smem_desc_sw128(k_addr + off, 16, 1024);
-                        mma_ss(tS0 + t * 128, da, db, idesc_s, ks > 0 ? 1u : 0u);
+                        // the address field counts 16-byte units and cannot carry out of its bits
+                        const uint32_t off16 = ((ks >> 2) * SUB + (ks & 3) * 32) >> 4;
+                        mma_ss(tS0 + t * 128, da0 + off16, db0 + off16, idesc_s, ks > 0 ? 1u : 0u);
                     }
                 };
                 // O_t += P_t V : A = P in tensor memory (two 16-bit values per column),
@@ -404,11 +416,11 @@ fa_mask_fwd_kernel(const __grid_constant__ CUtensorMap tm_q,
                 // P arrives in two halves of 64 keys: the first half's MMAs run while the
                 // softmax threads are still producing the second.
                 auto issue_pv_half = [&](int t, uint32_t v_addr, bool acc, int half) {
+                    const uint64_t dv0 = smem_desc_sw128(v_addr, SUB, 1024);
 #pragma unroll
                     for (int kk = 0; kk < kBlockN / 32; ++kk) {
                         const int ks = half * (kBlockN / 32) + kk;
-                        const uint64_t db = smem_desc_sw128(v_addr + ks * 2048, SUB, 1024);
-                        mma_ts(tO0 + t * 128, tS0 + t * 128 + ks * 8, db, idesc_o,
+                        mma_ts(tO0 + t * 128, tS0 + t * 128 + ks * 8, dv0 + ((ks * 2048) >> 4), idesc_o,
                                (acc || ks > 0) ? 1u : 0u);
                     }
                 };
@@ -1016,6 +1028,17 @@ struct DeviceGuard {
 static inline size_t align256(size_t x) { return (x + 255) & ~static_cast<size_t>(255); }
 static inline int ceil_div(int a, int b) { return (a + b - 1) / b; }
 
+// Every failed CUDA runtime call leaves through here: the error is cleared (a launch-time
+// error must not poison the caller's next call) and, with FA_SM100_DEBUG set in the
+// environment, named on stderr together with the source line that saw it.
+static int cuda_failed(int line) {
+    const cudaError_t err = cudaGetLastError();
+    static const bool verbose = std::getenv("FA_SM100_DEBUG") != nullptr;
+    if (verbose)
+        std::fprintf(stderr, "fa_mask_fwd_sm100: CUDA error at line %d: %s\n", line, cudaGetErrorString(err));
+    return FA_SM100_ERR_CUDA;
+}
+
 static int validate(const FaMaskFwdArgs* a) {
     if (a == nullptr) return FA_SM100_ERR_NULL;
     if (a->struct_size != sizeof(FaMaskFwdArgs)) return FA_SM100_ERR_ABI;
@@ -1141,8 +1164,7 @@ static int get_encode() {
     cudaDriverEntryPointQueryResult qres;
     if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres) != cudaSuccess ||
         qres != cudaDriverEntryPointSuccess || fn == nullptr) {
-        cudaGetLastError();
-        return FA_SM100_ERR_CUDA;
+        return cuda_failed(__LINE__);
     }
     g_encode = reinterpret_cast<EncodeTiledFn>(fn);
     return FA_SM100_OK;
@@ -1224,14 +1246,16 @@ static int launch_fwd(DeviceInfo* dev, int slot, const CUtensorMap& tq, const CU
         // The in-kernel register re-balancing is only sound for the register count it was
         // written for; refuse to launch a build that came out different.
         cudaFuncAttributes fattr;
-        if (cudaFuncGetAttributes(&fattr, kern) != cudaSuccess || fattr.numRegs != kLaunchRegs) {
-            cudaGetLastError();
+        if (cudaFuncGetAttributes(&fattr, kern) != cudaSuccess) return cuda_failed(__LINE__);
+        if (fattr.numRegs != kLaunchRegs) {
+            if (std::getenv("FA_SM100_DEBUG") != nullptr)
+                std::fprintf(stderr, "fa_mask_fwd_sm100: kernel built with %d registers, expected %d\n",
+                             fattr.numRegs, kLaunchRegs);
             return FA_SM100_ERR_CUDA;
         }
         if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  static_cast<int>(Cfg<D>::kSmemBytes)) != cudaSuccess) {
-            cudaGetLastError();
-            return FA_SM100_ERR_CUDA;
+            return cuda_failed(__LINE__);
         }
         dev->attr_set[slot] = true;
     }
@@ -1248,14 +1272,13 @@ static int launch_fwd(DeviceInfo* dev, int slot, const CUtensorMap& tq, const CU
         cfg.attrs = attr;
         cfg.numAttrs = 1;
         if (cudaLaunchKernelEx(&cfg, kern, tq, tk, tv, tm, kp) != cudaSuccess) {
-            cudaGetLastError();
-            return FA_SM100_ERR_CUDA;
+            return cuda_failed(__LINE__);
         }
         ++g_launches;
         return FA_SM100_OK;
     }
     kern<<<grid, kThreads, Cfg<D>::kSmemBytes, stream>>>(tq, tk, tv, tm, kp);
-    if (cudaGetLastError() != cudaSuccess) return FA_SM100_ERR_CUDA;
+    if (cudaPeekAtLastError() != cudaSuccess) return cuda_failed(__LINE__);
     ++g_launches;
     return FA_SM100_OK;
 }
@@ -1287,8 +1310,7 @@ static int launch_combine(const float* o_parts, const float* lse_parts, void* ou
             : cudaLaunchKernelEx(&cfg, fa_mask_combine_kernel<64>, o_parts, lse_parts, out, lse_out,
                                  parts, rows, is_bf16, out_fp32);
         if (e != cudaSuccess) {
-            cudaGetLastError();
-            return FA_SM100_ERR_CUDA;
+            return cuda_failed(__LINE__);
         }
         ++g_launches;
         return FA_SM100_OK;
@@ -1299,7 +1321,7 @@ static int launch_combine(const float* o_parts, const float* lse_parts, void* ou
     else
         fa_mask_combine_kernel<64><<<blocks, warps * 32, 0, stream>>>(
             o_parts, lse_parts, out, lse_out, parts, rows, dtype == FA_SM100_BF16, out_fp32);
-    if (cudaGetLastError() != cudaSuccess) return FA_SM100_ERR_CUDA;
+    if (cudaPeekAtLastError() != cudaSuccess) return cuda_failed(__LINE__);
     ++g_launches;
     return FA_SM100_OK;
 }
@@ -1308,8 +1330,7 @@ static int status_pointer(DeviceInfo* dev) {
     if (dev->status_ptr == nullptr) {
         void* ptr = nullptr;
         if (cudaGetSymbolAddress(&ptr, g_fa_status) != cudaSuccess) {
-            cudaGetLastError();
-            return FA_SM100_ERR_CUDA;
+            return cuda_failed(__LINE__);
         }
         dev->status_ptr = static_cast<unsigned int*>(ptr);
     }
@@ -1423,8 +1444,7 @@ static int forward(const FaMaskFwdArgs* a, void* workspace, size_t workspace_byt
 
     DeviceGuard guard(a->device);
     if (guard.err != cudaSuccess) {
-        cudaGetLastError();
-        return FA_SM100_ERR_CUDA;
+        return cuda_failed(__LINE__);
     }
     DeviceInfo* dev = nullptr;
     query_device(a->device, &dev);
@@ -1466,7 +1486,7 @@ static int forward(const FaMaskFwdArgs* a, void* workspace, size_t workspace_byt
         const unsigned blocks = static_cast<unsigned>(a->batch) * a->seqlen_q;
         fa_mask_repitch_kernel<<<blocks, 256, 0, stream>>>(
             mask_ptr, dst, a->seqlen_q, a->seqlen_k, pitch, mask_bs, mask_rs);
-        if (cudaGetLastError() != cudaSuccess) return FA_SM100_ERR_CUDA;
+        if (cudaPeekAtLastError() != cudaSuccess) return cuda_failed(__LINE__);
         ++g_launches;
         mask_ptr = dst;
         mask_bs = static_cast<long long>(a->seqlen_q) * pitch;
@@ -1491,8 +1511,7 @@ static int forward(const FaMaskFwdArgs* a, void* workspace, size_t workspace_byt
         cfg.numAttrs = plan.mask_repitched ? 1 : 0;      // chained behind the re-pitch kernel
         if (cudaLaunchKernelEx(&cfg, fa_mask_classify_kernel, mask_ptr, mask_bs, mask_rs, a->seqlen_q,
                                a->seqlen_k, ninf, flags, hint_counter) != cudaSuccess) {
-            cudaGetLastError();
-            return FA_SM100_ERR_CUDA;
+            return cuda_failed(__LINE__);
         }
         ++g_launches;
         kp.block_flags = flags;
@@ -1568,13 +1587,11 @@ static int forward_static_scratch(const FaMaskFwdArgs* a, cudaStream_t stream) {
             // set-up, once per device, with that device current
             DeviceGuard guard(a->device);
             if (guard.err != cudaSuccess) {
-                cudaGetLastError();
-                return FA_SM100_ERR_CUDA;
+                return cuda_failed(__LINE__);
             }
             void* ptr = nullptr;
             if (cudaGetSymbolAddress(&ptr, g_static_scratch) != cudaSuccess || ptr == nullptr) {
-                cudaGetLastError();
-                return FA_SM100_ERR_CUDA;
+                return cuda_failed(__LINE__);
             }
             g_static_scratch_addr[a->device] = ptr;
             scratch = ptr;
@@ -1623,8 +1640,7 @@ int fa_mask_fwd_sm100_combine(const float* o_parts, const float* lse_parts, void
     if (rows < 0 || device < 0 || device >= fa_sm100::kMaxDevices) return FA_SM100_ERR_SHAPE;
     fa_sm100::DeviceGuard guard(device);
     if (guard.err != cudaSuccess) {
-        cudaGetLastError();
-        return FA_SM100_ERR_CUDA;
+        return fa_sm100::cuda_failed(__LINE__);
     }
     return fa_sm100::launch_combine(o_parts, lse_parts, out, lse_out, num_parts, rows, head_dim,
                                     dtype, out_fp32, static_cast<cudaStream_t>(stream));
@@ -1635,24 +1651,20 @@ int fa_mask_fwd_sm100_device_status(int32_t device, uint32_t* status, int32_t cl
     if (device < 0 || device >= fa_sm100::kMaxDevices) return FA_SM100_ERR_SHAPE;
     fa_sm100::DeviceGuard guard(device);
     if (guard.err != cudaSuccess) {
-        cudaGetLastError();
-        return FA_SM100_ERR_CUDA;
+        return fa_sm100::cuda_failed(__LINE__);
     }
     unsigned int v = 0;
     if (cudaDeviceSynchronize() != cudaSuccess) {
-        cudaGetLastError();
-        return FA_SM100_ERR_CUDA;
+        return fa_sm100::cuda_failed(__LINE__);
     }
     if (cudaMemcpyFromSymbol(&v, fa_sm100::g_fa_status, sizeof(v)) != cudaSuccess) {
-        cudaGetLastError();
-        return FA_SM100_ERR_CUDA;
+        return fa_sm100::cuda_failed(__LINE__);
     }
     *status = v;
     if (clear && v != 0) {
         const unsigned int zero = 0;
         if (cudaMemcpyToSymbol(fa_sm100::g_fa_status, &zero, sizeof(zero)) != cudaSuccess) {
-            cudaGetLastError();
-            return FA_SM100_ERR_CUDA;
+            return fa_sm100::cuda_failed(__LINE__);
         }
     }
     return v == 0 ? FA_SM100_OK : FA_SM100_ERR_DEVICE_WAIT;
