@@ -2,15 +2,19 @@
 //
 //   O = softmax(Q K^T / sqrt(d) + M) V        (M additive: 0, -inf or a finite bias)
 //
-// One CTA owns up to two 128-row query tiles of one (batch, head) and walks a
-// range of 128-key blocks.  Roles inside the CTA (12 warps):
+// A unit of work is up to two 128-row query tiles of one (batch, head) and a range
+// of 128-key blocks.  The kernel is persistent: one CTA per SM works through its
+// units in turn, and the loads and the first MMA of the next unit run under the
+// epilogue of the current one.  Roles inside the CTA (12 warps):
 //
 //   warps 0-3   softmax group of query tile 0   (thread <-> query row)
 //   warps 4-7   softmax group of query tile 1
 //   warp  8     MMA issuer: one thread issues tcgen05.mma; also owns tensor memory
 //   warp  9     TMA producer for Q, K, V tiles
 //   warp 10     TMA producer for the mask tiles
-//   warp 11     idle (completes the warpgroup for the register re-balancing)
+//   warp 11     unit scheduler: decodes the next unit (and, with tile skipping, its
+//               list of key blocks to visit) one unit ahead and publishes it in
+//               shared memory for the other roles
 //
 // Everything the tensor cores and the softmax threads touch arrives through TMA
 // into 128-byte-swizzled shared memory behind mbarrier rings: Q (resident), a
@@ -69,8 +73,8 @@ constexpr int kThreads = 384;
 // setmaxnreg.inc can only take what setmaxnreg.dec released inside the same CTA, and it
 // blocks until that is there, so the books must balance or the softmax warps wait forever.
 constexpr int kLaunchRegs = 168;
-constexpr int kSoftmaxRegs = 224;
-constexpr int kOtherRegs = 56;        // warps 8-11: one warpgroup, which must ask for one common count
+constexpr int kSoftmaxRegs = 216;
+constexpr int kOtherRegs = 64;        // warps 8-11: one warpgroup, which must ask for one common count
 static_assert(8 * (kSoftmaxRegs - kLaunchRegs) <= 4 * (kLaunchRegs - kOtherRegs),
               "setmaxnreg.inc would ask for more registers than setmaxnreg.dec releases");
 static_assert(kThreads * kLaunchRegs <= 65536, "launch register budget");
@@ -80,7 +84,7 @@ static_assert(kThreads * kLaunchRegs <= 65536, "launch register budget");
 static_assert(2 * kSoftmaxRegs + kOtherRegs <= 512,
               "a scheduler's quarter of the register file cannot hold its three warps");
 constexpr uint32_t kTmemCols = 512;
-constexpr int kMaxListBlocks = 512;    // key blocks a CTA can keep a skip list for (Sk <= 65536)
+constexpr int kMaxListBlocks = 384;    // key blocks a CTA can keep a skip list for (Sk <= 49152)
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kRescaleThreshold = 5.545177444479562f;   // 8 * ln 2: rescale when max grew > 2^8
 constexpr uint32_t kPanelBytes = 128 * 64 * 2;            // 128 rows x 64 columns, 16 bit
@@ -88,7 +92,7 @@ constexpr uint32_t kPanelBytes = 128 * 64 * 2;            // 128 rows x 64 colum
 // Status codes written to the device status word when a bounded wait runs out.
 enum : uint32_t {
     kStTmaEmpty = 1, kStMmaQ = 2, kStMmaKv = 3, kStMmaP = 4, kStSoftmaxS = 5, kStSoftmaxO = 6,
-    kStDrain = 7, kStMaskEmpty = 8, kStSoftmaxMask = 9
+    kStDrain = 7, kStMaskEmpty = 8, kStSoftmaxMask = 9, kStList = 10
 };
 
 __device__ unsigned int g_fa_status = 0;
@@ -100,8 +104,8 @@ struct Cfg {
     static constexpr uint32_t kSubBytes = kPanelBytes;            // 64-column swizzle panel
     static constexpr int kSub = D / 64;
     static constexpr uint32_t kMaskBytes = 4 * kPanelBytes;       // 2 tiles x 2 panels
-    static constexpr uint32_t kBarBytes = 320;
-    static constexpr uint32_t kListBytes = kMaxListBlocks * 2;   // compacted key-block list (uint16)
+    static constexpr uint32_t kBarBytes = 512;            // mbarriers, small words, two unit boards
+    static constexpr uint32_t kListBytes = 2 * kMaxListBlocks * 2;   // two compacted key-block lists (uint16)
     static constexpr uint32_t kSmemBytes =
         1024 + 2 * kTileBytes + kStages * kTileBytes + kMaskBytes + kBarBytes + kListBytes;
     static_assert(kSmemBytes <= 227 * 1024, "more shared memory than a CTA can have");
@@ -116,11 +120,14 @@ struct KParams {
     int B, H, Hk, Sq, Sk;
     int num_splits, kv_blocks;
     int m_pairs;              // 256-row query pairs per (batch, head)
+    int total_units;          // B * H * m_pairs * split_groups; a CTA takes every gridDim.x-th one
     int split_groups;         // CTAs along the split axis: num_splits, or ceil(num_splits/2) in dual mode
     int dual;                 // 1: one query tile, two KV splits per CTA
+    unsigned int* unit_counter;         // with block_flags: units taken beyond the first of each CTA
     const unsigned char* block_flags;   // (B, m_pairs, kv_blocks): 0 = every key of the block is
                                         // masked (-inf) for all 256 rows -> skipped; NULL = no skipping
     int out_fp32;
+    int wide_stores;          // 1: out and the partials are 32-byte aligned (256-bit stores)
     float scale;              // 1 / sqrt(d)
 };
 
@@ -139,6 +146,75 @@ __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
     else return pack_f16x2(lo, hi);
 }
 
+// Unit board: what the scheduler warp publishes about one unit of work, a (split group,
+// 256-row query pair, head, batch) combination, as ints in shared memory.  A CTA runs two
+// softmax/MMA streams ("slots"); words kUiSlot + 4 * t + ... describe slot t.
+enum : int {
+    kUiB = 0, kUiH = 1, kUiSgroup = 2, kUiKvPlane = 3, kUiQPlane = 4,
+    kUiUnit = 5,    // index of the unit; -1: no more work for this CTA
+    kUiSlot = 8,
+    kUiSplit = 0,   // KV split the slot covers
+    kUiBegin = 1,   // first key block
+    kUiN = 2,       // key blocks to visit; 0: nothing visible; -1: the slot does not exist
+    kUiRow0 = 3,    // first query row
+    kUiInts = 16
+};
+
+// Epilogue helper.  Each softmax thread owns one output row, so a plain store instruction of
+// a warp touches 32 different rows, 32 memory transactions of 16 or 32 bytes each, and the
+// epilogue was bound by that.  Here the four lanes of a quad (four consecutive rows) first
+// transpose 32-byte blocks among themselves: w[0..31] holds 128 contiguous bytes of the
+// lane's own row on entry; on return w[8i..8i+7] holds block q = lane % 4 of the row of quad
+// lane i.  Store i of the four lanes of a quad then writes one full 128-byte line of row i.
+__device__ __forceinline__ void quad_transpose(uint32_t (&w)[32], int lane) {
+    const bool odd1 = (lane & 1) != 0;
+    const bool odd2 = (lane & 2) != 0;
+    // step 1, partner lane ^ 1: of each pair of blocks (0,1) and (2,3) a lane keeps the one
+    // with its own parity and swaps the other
+#pragma unroll
+    for (int b = 0; b < 4; b += 2) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const uint32_t send = odd1 ? w[8 * b + i] : w[8 * (b + 1) + i];
+            const uint32_t recv = __shfl_xor_sync(0xffffffffu, send, 1);
+            if (odd1) w[8 * b + i] = recv;
+            else w[8 * (b + 1) + i] = recv;
+        }
+    }
+    // step 2, partner lane ^ 2: the same with the pairs of positions (0,1) and (2,3) as units
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+        const uint32_t send = odd2 ? w[i] : w[16 + i];
+        const uint32_t recv = __shfl_xor_sync(0xffffffffu, send, 2);
+        if (odd2) w[i] = recv;
+        else w[16 + i] = recv;
+    }
+}
+
+// Writes the transposed blocks: `row_ptr` = address of the 128-byte piece of the lane's OWN
+// row, `row_bytes` = distance between consecutive rows, `rows_left` = valid rows counted from
+// the lane's own row (<= 0: the lane's row is out of range).
+__device__ __forceinline__ void quad_store(const uint32_t (&w)[32], int lane, char* row_ptr, long long row_bytes,
+                                           int rows_left) {
+    const int q = lane & 3;
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+        if (i - q < rows_left) stg256(row_ptr + (i - q) * row_bytes + q * 32, &w[8 * i]);
+}
+
+// Cursor over a ring of mbarrier-guarded buffers: slot index and phase bit, advanced
+// without any division.
+struct Ring {
+    int slot = 0;
+    uint32_t phase = 0;
+    __device__ __forceinline__ void advance(int slots) {
+        if (++slot == slots) {
+            slot = 0;
+            phase ^= 1u;
+        }
+    }
+};
+
 template <int D, bool BF16, bool LIST>
 __global__ void __launch_bounds__(kThreads, 1)
 fa_mask_fwd_kernel(const __grid_constant__ CUtensorMap tm_q,
@@ -156,72 +232,51 @@ fa_mask_fwd_kernel(const __grid_constant__ CUtensorMap tm_q,
     const uint32_t base = (raw_u32 + 1023u) & ~1023u;
     const uint32_t sQ = base;
     const uint32_t sKV = sQ + 2 * TILE;
-    const uint32_t sM = sKV + NS * TILE;               // [tile][panel] of kPanelBytes
+    const uint32_t sM = sKV + NS * TILE;               // [slot][panel] of kPanelBytes
     const uint32_t sBar = sM + C::kMaskBytes;
-    const uint32_t bar_q_full = sBar;                  // [2]
-    const uint32_t bar_s_full = sBar + 16;             // [2]
+    // mbarriers (8 bytes each)
+    const uint32_t bar_q_full = sBar;                  // [2] Q tile landed
+    const uint32_t bar_s_full = sBar + 16;             // [2] S of a slot computed
     const uint32_t bar_p_ready = sBar + 32;            // [2] first 64 keys of P written
-    const uint32_t bar_p_ready2 = sBar + 256;          // [2] last 64 keys of P written
-    const uint32_t bar_merge = sBar + 272;             // dual mode: both slots have their final O
-    const uint32_t bar_o_full = sBar + 48;             // [2]
-    const uint32_t bar_m_full = sBar + 64;             // [4]
-    const uint32_t bar_m_empty = sBar + 96;            // [4]
-    const uint32_t bar_kv_full = sBar + 128;           // [NS + 1] (dual mode has one slot more)
-    const uint32_t bar_kv_empty = sBar + 128 + 8 * (NS + 1); // [NS + 1]
-    const uint32_t tmem_slot_addr = sBar + 128 + 16 * (NS + 1);
-    const uint32_t sList = sBar + C::kBarBytes;          // uint16 [kMaxListBlocks]
-    uint8_t* bar_generic = smem_raw + (sBar - raw_u32);
-    volatile uint16_t* blk_list = reinterpret_cast<volatile uint16_t*>(bar_generic + C::kBarBytes);
-    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(bar_generic + 128 + 16 * (NS + 1));
-    volatile uint32_t* abort_flag = tmem_slot + 1;
-    volatile int* list_count = reinterpret_cast<volatile int*>(tmem_slot + 2);
+    const uint32_t bar_o_full = sBar + 48;             // [2] last P.V of a unit done
+    const uint32_t bar_m_full = sBar + 64;             // [4] mask panel landed
+    const uint32_t bar_m_empty = sBar + 96;            // [4] mask panel consumed
+    const uint32_t bar_kv_full = sBar + 128;           // [NS + 1] K/V ring (dual mode: one slot more)
+    const uint32_t bar_kv_empty = sBar + 128 + 8 * (NS + 1);
+    const uint32_t bar_p_ready2 = sBar + 240;          // [2] last 64 keys of P written
+    const uint32_t bar_merge = sBar + 256;             // dual mode: both slots hold their final O
+    const uint32_t bar_q_free = sBar + 264;            // [2] every S MMA that reads the Q tile is done
+    const uint32_t bar_unit_full = sBar + 288;         // [2] unit board (and skip list) published
+    const uint32_t bar_unit_empty = sBar + 304;        // [2] ... and no longer needed
+    // small words, all addressed in the shared space (one register each, not two)
+    const uint32_t tmem_slot_addr = sBar + 320;        // tensor-memory base written by tcgen05.alloc
+    const uint32_t abort_flag = sBar + 324;            // set once a bounded wait of this CTA gave up
+    const uint32_t bail_word = sBar + 328;
+    const uint32_t unit_board = sBar + 384;            // [2][kUiInts] ints
+    const uint32_t blk_list = sBar + C::kBarBytes;     // [2][kMaxListBlocks] uint16
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
 
     // Once any CTA of any launch gave up on a wait, the status word stays set until
     // the host clears it; later CTAs leave at once so a broken launch drains quickly.
-    __shared__ uint32_t s_bail;
-    if (threadIdx.x == 0) s_bail = *reinterpret_cast<volatile unsigned int*>(p.status);
+    if (threadIdx.x == 0) sts32(bail_word, *reinterpret_cast<volatile unsigned int*>(p.status));
     __syncthreads();
-    if (s_bail != 0) return;
+    if (lds32(bail_word) != 0) return;
 
-    // Work decode: blockIdx.x enumerates (split group, 256-row query pair, head, batch), split
-    // group fastest.  The CTA runs two independent softmax/MMA streams ("slots"):
+    // The CTA is persistent in pair mode: it takes units blockIdx.x, blockIdx.x + gridDim.x, ...
+    // and every role keeps running counters for its barrier phases, so the producers and the
+    // MMA thread run into the next unit (Q and K loads, first S = Q K^T) while the softmax
+    // groups are still writing the previous unit's output.  Slots of a unit:
     //   pair mode  slot t = query tile t of the pair; both slots walk the same key blocks and
     //              share every K/V tile in shared memory;
-    //   dual mode  (one query tile only, Split-KV) slot t = KV split 2*group + t of the SAME
-    //              query tile: two key ranges stream side by side, so a CTA that would
-    //              otherwise leave half of its softmax threads idle pulls twice the bytes.
-    int unit = blockIdx.x;
-    const int sgroup = unit % p.split_groups;
-    unit /= p.split_groups;
-    const int mpair = unit % p.m_pairs;
-    unit /= p.m_pairs;
-    const int h = unit % p.H;
-    const int b = unit / p.H;
-    const int hk = h / (p.H / p.Hk);
-    const int m0 = mpair * (2 * kBlockM);
+    //   dual mode  (one query tile only, Split-KV; one unit per CTA) slot t = KV split
+    //              2*group + t of the SAME query tile: two key ranges stream side by side.
     const bool dual = p.dual != 0;
-    // Tile skipping (single-pass pair mode only): a pre-pass marked the key blocks whose mask
-    // is -inf for all 256 rows of this pair.  The idle warp compacts the flags into a list of
-    // the blocks to visit; every role then walks the list instead of 0..kv_blocks-1.  Skipping
-    // such a block is exact: all of its weights would be 0.
-    constexpr bool use_list = LIST;        // compiled twice: with and without the skip list
-    if (use_list && warp == 11) {
-        pdl_wait_prior_grid();                 // the flags come from the pre-pass kernel
-        const unsigned char* fl = p.block_flags +
-            (static_cast<long long>(b) * p.m_pairs + mpair) * p.kv_blocks;
-        int count = 0;
-        for (int base_j = 0; base_j < p.kv_blocks; base_j += 32) {
-            const int jj = base_j + lane;
-            const bool need = jj < p.kv_blocks && fl[jj] != 0;
-            const unsigned ballot = __ballot_sync(0xffffffffu, need);
-            if (need) blk_list[count + __popc(ballot & ((1u << lane) - 1u))] = static_cast<uint16_t>(jj);
-            count += __popc(ballot);
-        }
-        if (lane == 0) *list_count = count;
-    }
+    // dual mode needs one Q tile only: the second Q buffer becomes a fourth K/V ring slot
+    const uint32_t ring_base = dual ? sKV - TILE : sKV;
+    const int ring_slots = dual ? NS + 1 : NS;
+    constexpr int kUnitConsumers = 3 + 8;   // two producers, MMA thread, lane 0 of each softmax warp
 
     if (warp == kTmaWarp && lane == 0) {
         for (int t = 0; t < 2; ++t) {
@@ -230,6 +285,9 @@ fa_mask_fwd_kernel(const __grid_constant__ CUtensorMap tm_q,
             mbar_init(bar_p_ready + 8 * t, kSoftmaxThreads);
             mbar_init(bar_p_ready2 + 8 * t, kSoftmaxThreads);
             mbar_init(bar_o_full + 8 * t, 1);
+            mbar_init(bar_q_free + 8 * t, 1);
+            mbar_init(bar_unit_full + 8 * t, 1);
+            mbar_init(bar_unit_empty + 8 * t, kUnitConsumers);
         }
         for (int i = 0; i < 4; ++i) {
             mbar_init(bar_m_full + 8 * i, 1);
@@ -240,7 +298,7 @@ fa_mask_fwd_kernel(const __grid_constant__ CUtensorMap tm_q,
             mbar_init(bar_kv_empty + 8 * i, 1);
         }
         mbar_init(bar_merge, 2 * kSoftmaxThreads);
-        *abort_flag = 0;
+        sts32(abort_flag, 0u);
         fence_barrier_init();
         prefetch_tensormap(&tm_q);
         prefetch_tensormap(&tm_k);
@@ -254,100 +312,108 @@ fa_mask_fwd_kernel(const __grid_constant__ CUtensorMap tm_q,
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
-    const uint32_t tmem_base = *tmem_slot;
+    const uint32_t tmem_base = lds32(tmem_slot_addr);
     pdl_launch_dependents();      // a chained merge kernel may start its prologue now
 
-    int sl_split[2], sl_begin[2], sl_n[2], sl_row0[2];
-    bool sl_on[2];
-#pragma unroll
-    for (int t = 0; t < 2; ++t) {
-        sl_split[t] = dual ? 2 * sgroup + t : sgroup;
-        // split s owns key blocks [s*nb/S, (s+1)*nb/S): sizes differ by at most one block
-        sl_begin[t] = static_cast<int>(static_cast<long long>(sl_split[t]) * p.kv_blocks / p.num_splits);
-        sl_row0[t] = dual ? m0 : m0 + t * kBlockM;
-        const int cnt = static_cast<int>(static_cast<long long>(sl_split[t] + 1) * p.kv_blocks /
-                                         p.num_splits) - sl_begin[t];
-        sl_on[t] = dual ? (sl_split[t] < p.num_splits) : (sl_row0[t] < p.Sq);
-        sl_n[t] = (sl_on[t] && cnt > 0) ? cnt : 0;
-        if (use_list) sl_n[t] = sl_on[t] ? *list_count : 0;   // may be 0: nothing visible at all
-    }
-    // key block visited at step j of slot t
-    auto blk = [&](int t, int j) -> int {
-        return use_list ? static_cast<int>(blk_list[j]) : sl_begin[t] + j;
+    // Board of the k-th unit of this CTA (shared-space address); 0 when the wait gave up.
+    auto unit_wait = [&](int k) -> uint32_t {
+        if (!mbar_wait(bar_unit_full + 8 * (k & 1), (k >> 1) & 1, abort_flag, p.status, kStList)) return 0u;
+        return unit_board + (k & 1) * (kUiInts * 4);
     };
-    const bool has_q1 = !dual && sl_n[1] > 0;
-    const int n = sl_n[0];
-    const int nmax = max(sl_n[0], sl_n[1]);
-    // dual mode needs one Q tile only: the second Q buffer becomes a fourth K/V ring slot
-    const uint32_t ring_base = dual ? sKV - TILE : sKV;
-    const int ring_slots = dual ? NS + 1 : NS;
-
+    // word i of a board, as an int
+    auto ui_get = [](uint32_t board, int i) -> int { return static_cast<int>(lds32(board + 4 * i)); };
+    auto unit_done = [&](int k) { mbar_arrive(bar_unit_empty + 8 * (k & 1)); };
 
     if (warp >= 8) {
         // Data-movement and MMA-issue warps need few registers; hand the rest to softmax.
+        // (setmaxnreg is a warpgroup-wide instruction: all four warps give the same count)
         reg_dealloc<kOtherRegs>();
         if (warp == kTmaWarp) {
             // -------------------------------------------------------------- Q/K/V producer
             if (lane == 0) {
-                const int q_plane = b * p.H + h;
-                const int kv_plane = b * p.Hk + hk;
-                if (n > 0) {
-                    mbar_arrive_expect_tx(bar_q_full, TILE);
-#pragma unroll
-                    for (int s = 0; s < C::kSub; ++s)
-                        tma_load_3d(sQ + s * SUB, &tm_q, bar_q_full, s * 64, m0, q_plane);
-                }
-                if (has_q1) {
-                    mbar_arrive_expect_tx(bar_q_full + 8, TILE);
-#pragma unroll
-                    for (int s = 0; s < C::kSub; ++s)
-                        tma_load_3d(sQ + TILE + s * SUB, &tm_q, bar_q_full + 8, s * 64,
-                                    m0 + kBlockM, q_plane);
-                }
+                Ring ring;                      // next ring slot to fill, over all units
+                int in_flight = 0;              // fills issued (capped), for the drain below
+                uint32_t q_phase[2] = {1u, 1u}; // parity that says "Q tile t may be overwritten"
+                bool ok = true;
+                int kv_plane = 0;
                 // One K or V tile into the next ring slot; false when a wait gave up.
-                int issued = 0;
                 auto fill = [&](bool is_v, int block) -> bool {
-                    const int f = issued;
-                    const int slot = f % ring_slots;
-                    if (f >= ring_slots &&
-                        !mbar_wait(bar_kv_empty + 8 * slot, ((f / ring_slots) - 1) & 1, abort_flag,
-                                   p.status, kStTmaEmpty))
+                    // a fresh barrier passes the wait for the phase before its first one
+                    if (!mbar_wait(bar_kv_empty + 8 * ring.slot, ring.phase ^ 1u, abort_flag, p.status,
+                                   kStTmaEmpty))
                         return false;
                     const CUtensorMap* tm = is_v ? &tm_v : &tm_k;
-                    const uint32_t dst = ring_base + slot * TILE;
-                    mbar_arrive_expect_tx(bar_kv_full + 8 * slot, TILE);
+                    const uint32_t dst = ring_base + ring.slot * TILE;
+                    const uint32_t bar = bar_kv_full + 8 * ring.slot;
+                    mbar_arrive_expect_tx(bar, TILE);
 #pragma unroll
                     for (int s = 0; s < C::kSub; ++s)
-                        tma_load_3d(dst + s * SUB, tm, bar_kv_full + 8 * slot, s * 64,
-                                    block * kBlockN, kv_plane);
-                    issued = f + 1;
+                        tma_load_3d(dst + s * SUB, tm, bar, s * 64, block * kBlockN, kv_plane);
+                    ring.advance(ring_slots);
+                    if (in_flight < ring_slots) ++in_flight;
                     return true;
                 };
-                bool ok = true;
-                if (!dual) {
-                    // shared by both slots: K_0, V_0, K_1, V_1, ...
-                    for (int j = 0; ok && j < n; ++j)
-                        ok = fill(false, blk(0, j)) && fill(true, blk(0, j));
-                } else {
-                    // the order the MMA thread consumes them: K_a0, K_b0, then per step
-                    // V_a(j), K_a(j+1), V_b(j), K_b(j+1)
-                    ok = fill(false, sl_begin[0]);
-                    if (ok && sl_n[1] > 0) ok = fill(false, sl_begin[1]);
-                    for (int j = 0; ok && j < nmax; ++j) {
+                int k = 0;
+                for (; ok; ++k) {
+                    const uint32_t ui = unit_wait(k);
+                    if (!(ok = (ui != 0u)) || ui_get(ui, kUiUnit) < 0) break;
+                    const uint32_t lst = blk_list + (k & 1) * (kMaxListBlocks * 2);
+                    const int n0 = max(ui_get(ui, kUiSlot + kUiN), 0);
+                    const int n1 = max(ui_get(ui, kUiSlot + 4 + kUiN), 0);
+                    const int begin0 = ui_get(ui, kUiSlot + kUiBegin), begin1 = ui_get(ui, kUiSlot + 4 + kUiBegin);
+                    const bool has_q1 = !dual && n1 > 0;
+                    kv_plane = ui_get(ui, kUiKvPlane);
+                    if (n0 > 0) {
+                        const int q_plane = ui_get(ui, kUiQPlane);
 #pragma unroll
                         for (int t = 0; t < 2; ++t) {
-                            if (ok && j < sl_n[t]) ok = fill(true, sl_begin[t] + j);
-                            if (ok && j + 1 < sl_n[t]) ok = fill(false, sl_begin[t] + j + 1);
+                            if (!ok || (t == 1 && !has_q1)) continue;
+                            // the tile may still be read by the previous unit's last S = Q K^T
+                            if (!(ok = mbar_wait(bar_q_free + 8 * t, q_phase[t], abort_flag, p.status,
+                                                 kStTmaEmpty)))
+                                continue;
+                            q_phase[t] ^= 1u;
+                            mbar_arrive_expect_tx(bar_q_full + 8 * t, TILE);
+#pragma unroll
+                            for (int s = 0; s < C::kSub; ++s)
+                                tma_load_3d(sQ + t * TILE + s * SUB, &tm_q, bar_q_full + 8 * t, s * 64,
+                                            ui_get(ui, kUiSlot + 4 * t + kUiRow0), q_plane);
+                        }
+                        if (!dual) {
+                            // shared by both slots: K_0, V_0, K_1, V_1, ...
+                            for (int j = 0; ok && j < n0; ++j) {
+                                const int blk = LIST ? static_cast<int>(lds16(lst + 2 * j)) : begin0 + j;
+                                ok = fill(false, blk) && fill(true, blk);
+                            }
+                        } else {
+                            // the order the MMA thread consumes them: K_a0, K_b0, then per step
+                            // V_a(j), K_a(j+1), V_b(j), K_b(j+1)
+                            const int nmax = max(n0, n1);
+                            ok = ok && fill(false, begin0);
+                            if (ok && n1 > 0) ok = fill(false, begin1);
+                            for (int j = 0; ok && j < nmax; ++j) {
+                                if (ok && j < n0) ok = fill(true, begin0 + j);
+                                if (ok && j + 1 < n0) ok = fill(false, begin0 + j + 1);
+                                if (ok && j < n1) ok = fill(true, begin1 + j);
+                                if (ok && j + 1 < n1) ok = fill(false, begin1 + j + 1);
+                            }
                         }
                     }
+                    unit_done(k);
                 }
-                if (*abort_flag) {
+                if (lds32(abort_flag) != 0u) {
                     // Giving up: let the copies already in flight land before the CTA exits.
-                    for (int f = max(0, issued - ring_slots); f < issued; ++f) {
-                        const uint32_t bar = bar_kv_full + 8 * (f % ring_slots);
-                        const uint32_t par = (f / ring_slots) & 1;
+                    // Walk back over the last fills; the slot before `ring` was filled last.
+                    Ring r = ring;
+                    for (int i = 0; i < in_flight; ++i) {
+                        if (r.slot == 0) {
+                            r.slot = ring_slots;
+                            r.phase ^= 1u;
+                        }
+                        --r.slot;
                         bool done = false;
-                        for (uint32_t i = 0; i < kMaxPolls && !done; ++i) done = mbar_try_wait(bar, par);
+                        for (uint32_t it = 0; it < kMaxPolls && !done; ++it)
+                            done = mbar_try_wait(bar_kv_full + 8 * r.slot, r.phase);
                         if (!done) atomicMax(p.status, static_cast<unsigned int>(kStDrain));
                     }
                 }
@@ -360,33 +426,136 @@ fa_mask_fwd_kernel(const __grid_constant__ CUtensorMap tm_q,
                 // everything that does not need the mask has already started.
                 pdl_wait_prior_grid();
                 // Panel i = slot * 2 + half.  A slot's panels follow that slot's own key blocks.
-                int last_j[2] = {-1, -1};
+                uint32_t ph[4] = {0u, 0u, 0u, 0u};      // phase of panel i's next load
+                bool sent[4] = {false, false, false, false};
                 bool ok = true;
-                for (int j = 0; ok && j < nmax; ++j) {
-                    for (int i = 0; ok && i < 4; ++i) {
-                        const int t = i >> 1;
-                        if (j >= sl_n[t]) continue;
-                        if (j > 0 && !mbar_wait(bar_m_empty + 8 * i, (j - 1) & 1, abort_flag,
-                                                p.status, kStMaskEmpty)) {
-                            ok = false;
-                            break;
+                int k = 0;
+                for (; ok; ++k) {
+                    const uint32_t ui = unit_wait(k);
+                    if (!(ok = (ui != 0u)) || ui_get(ui, kUiUnit) < 0) break;
+                    const uint32_t lst = blk_list + (k & 1) * (kMaxListBlocks * 2);
+                    const int n_of[2] = {max(ui_get(ui, kUiSlot + kUiN), 0), max(ui_get(ui, kUiSlot + 4 + kUiN), 0)};
+                    const int begin_of[2] = {ui_get(ui, kUiSlot + kUiBegin), ui_get(ui, kUiSlot + 4 + kUiBegin)};
+                    const int row0_of[2] = {ui_get(ui, kUiSlot + kUiRow0), ui_get(ui, kUiSlot + 4 + kUiRow0)};
+                    const int b = ui_get(ui, kUiB);
+                    const int nmax = max(n_of[0], n_of[1]);
+                    for (int j = 0; ok && j < nmax; ++j) {
+#pragma unroll
+                        for (int t = 0; t < 2; ++t) {
+                            if (!ok || j >= n_of[t]) continue;
+                            const int blk = LIST ? static_cast<int>(lds16(lst + 2 * j)) : begin_of[t] + j;
+#pragma unroll
+                            for (int hf = 0; hf < 2; ++hf) {
+                                const int i = 2 * t + hf;
+                                if (!ok) continue;
+                                if (!(ok = mbar_wait(bar_m_empty + 8 * i, ph[i] ^ 1u, abort_flag, p.status,
+                                                     kStMaskEmpty)))
+                                    continue;
+                                mbar_arrive_expect_tx(bar_m_full + 8 * i, kPanelBytes);
+                                tma_load_3d(sM + i * kPanelBytes, &tm_m, bar_m_full + 8 * i,
+                                            blk * kBlockN + hf * 64, row0_of[t], b);
+                                ph[i] ^= 1u;
+                                sent[i] = true;
+                            }
                         }
-                        mbar_arrive_expect_tx(bar_m_full + 8 * i, kPanelBytes);
-                        tma_load_3d(sM + i * kPanelBytes, &tm_m, bar_m_full + 8 * i,
-                                    blk(t, j) * kBlockN + (i & 1) * 64, sl_row0[t], b);
-                        if (i & 1) last_j[t] = j;
                     }
+                    unit_done(k);
                 }
-                if (*abort_flag) {
+                if (lds32(abort_flag) != 0u) {
+#pragma unroll
                     for (int i = 0; i < 4; ++i) {
-                        const int lj = last_j[i >> 1];
-                        if (lj < 0) continue;
+                        if (!sent[i]) continue;
                         bool done = false;
                         for (uint32_t it = 0; it < kMaxPolls && !done; ++it)
-                            done = mbar_try_wait(bar_m_full + 8 * i, lj & 1);
+                            done = mbar_try_wait(bar_m_full + 8 * i, ph[i] ^ 1u);
                         if (!done) atomicMax(p.status, static_cast<unsigned int>(kStDrain));
                     }
                 }
+            }
+        } else if (warp == 11) {
+            // -------------------------------------------------------------- unit scheduler
+            // Decodes the CTA's units one ahead of the roles that work on them and publishes
+            // each on the unit board, so the integer divisions of the decode are paid once, off
+            // every critical path.  With tile skipping (single-pass pair mode only) it also
+            // compacts the unit's block flags - a pre-pass kernel marked the key blocks whose
+            // mask is -inf for all 256 rows of a pair - into the list of blocks to visit.
+            // Skipping such a block is exact: all of its weights are 0.
+            if constexpr (LIST) pdl_wait_prior_grid();     // the flags come from the pre-pass kernel
+            // Which unit comes next: a CTA starts with unit blockIdx.x; after that it takes every
+            // gridDim.x-th one, or - with tile skipping, where units differ in length - the next
+            // one nobody has taken yet, from a counter the pre-pass kernel reset.
+            int unit = blockIdx.x;
+            for (int k = 0;; ++k) {
+                // board k&1 was last used by unit k-2: a fresh barrier passes at once
+                const bool ok = mbar_wait(bar_unit_empty + 8 * (k & 1), ((k >> 1) & 1) ^ 1u, abort_flag,
+                                          p.status, kStList);
+                if (!__all_sync(0xffffffffu, ok)) break;
+                if (k > 0) {
+                    if (LIST) {
+                        if (lane == 0) unit = static_cast<int>(gridDim.x + atomicAdd(p.unit_counter, 1u));
+                        unit = __shfl_sync(0xffffffffu, unit, 0);
+                    } else {
+                        unit += gridDim.x;
+                    }
+                }
+                if (unit >= p.total_units) {
+                    if (lane == 0) {
+                        sts32(unit_board + (k & 1) * (kUiInts * 4) + 4 * kUiUnit, 0xffffffffu);
+                        mbar_arrive(bar_unit_full + 8 * (k & 1));
+                    }
+                    break;
+                }
+                int rest = unit;
+                const int sgroup = rest % p.split_groups;
+                rest /= p.split_groups;
+                // later query pairs first: under causal-like masks they carry the most key blocks
+                const int mpair = p.m_pairs - 1 - (rest % p.m_pairs);
+                rest /= p.m_pairs;
+                const int h = rest % p.H;
+                const int b = rest / p.H;
+                int count = 0;
+                if constexpr (LIST) {
+                    const unsigned char* fl = p.block_flags +
+                        (static_cast<long long>(b) * p.m_pairs + mpair) * p.kv_blocks;
+                    const uint32_t lst = blk_list + (k & 1) * (kMaxListBlocks * 2);
+                    for (int base_j = 0; base_j < p.kv_blocks; base_j += 32) {
+                        const int jj = base_j + lane;
+                        const bool need = jj < p.kv_blocks && fl[jj] != 0;
+                        const unsigned ballot = __ballot_sync(0xffffffffu, need);
+                        if (need) sts16(lst + 2 * (count + __popc(ballot & ((1u << lane) - 1u))), static_cast<uint32_t>(jj));
+                        count += __popc(ballot);
+                    }
+                }
+                const uint32_t ui = unit_board + (k & 1) * (kUiInts * 4);
+                if (lane < 2) {
+                    // lane t describes slot t
+                    const int t = lane;
+                    const int m0 = mpair * (2 * kBlockM);
+                    const int split = dual ? 2 * sgroup + t : sgroup;
+                    // split s owns key blocks [s*nb/S, (s+1)*nb/S): sizes differ by at most one block
+                    const unsigned nb = static_cast<unsigned>(p.kv_blocks), ns = static_cast<unsigned>(p.num_splits);
+                    // (32 bits hold split * nb: at most 128 splits of at most 2^24 blocks)
+                    const int begin = static_cast<int>(static_cast<unsigned>(split) * nb / ns);
+                    const int end = static_cast<int>(static_cast<unsigned>(split + 1) * nb / ns);
+                    const int row0 = dual ? m0 : m0 + t * kBlockM;
+                    const bool on = dual ? (split < p.num_splits) : (row0 < p.Sq);
+                    int n = on ? max(end - begin, 0) : -1;                 // -1: the slot does not exist
+                    if (LIST && on) n = count;                             // may be 0: nothing visible at all
+                    sts32(ui + 4 * (kUiSlot + 4 * t + kUiSplit), static_cast<uint32_t>(split));
+                    sts32(ui + 4 * (kUiSlot + 4 * t + kUiBegin), static_cast<uint32_t>(begin));
+                    sts32(ui + 4 * (kUiSlot + 4 * t + kUiN), static_cast<uint32_t>(n));
+                    sts32(ui + 4 * (kUiSlot + 4 * t + kUiRow0), static_cast<uint32_t>(row0));
+                    if (t == 0) {
+                        sts32(ui + 4 * (kUiUnit), static_cast<uint32_t>(unit));
+                        sts32(ui + 4 * (kUiB), static_cast<uint32_t>(b));
+                        sts32(ui + 4 * (kUiH), static_cast<uint32_t>(h));
+                        sts32(ui + 4 * (kUiSgroup), static_cast<uint32_t>(sgroup));
+                        sts32(ui + 4 * (kUiKvPlane), static_cast<uint32_t>(b * p.Hk + h / (p.H / p.Hk)));
+                        sts32(ui + 4 * (kUiQPlane), static_cast<uint32_t>(b * p.H + h));
+                    }
+                }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bar_unit_full + 8 * (k & 1));    // release: board and list visible
             }
         } else if (warp == kMmaWarp) {
             // -------------------------------------------------------------- MMA issuer
@@ -395,6 +564,10 @@ fa_mask_fwd_kernel(const __grid_constant__ CUtensorMap tm_q,
                 constexpr uint32_t idesc_o = make_idesc(BF16, true, kBlockM, D);
                 const uint32_t tS0 = tmem_base;
                 const uint32_t tO0 = tmem_base + 256;
+                Ring ring;                      // next K/V tile to take, in the producer's order
+                uint32_t p_phase[2] = {0u, 0u}; // parity of slot t's next P hand-off
+                uint32_t q_phase[2] = {0u, 0u}; // parity of Q tile t's next arrival
+                bool ok = true;
 
                 // S_t = Q_t K^T : A and B both K-major, 64-column 128B-swizzled panels.
                 auto issue_s = [&](int t, uint32_t k_addr) {
@@ -412,9 +585,9 @@ fa_mask_fwd_kernel(const __grid_constant__ CUtensorMap tm_q,
                     }
                 };
                 // O_t += P_t V : A = P in tensor memory (two 16-bit values per column),
-                // B = V tile, d contiguous (MN-major), 16 keys per step.
-                // P arrives in two halves of 64 keys: the first half's MMAs run while the
-                // softmax threads are still producing the second.
+                // B = V tile, d contiguous (MN-major), 16 keys per step.  P arrives in two
+                // halves of 64 keys: the first half's MMAs run while the softmax threads are
+                // still producing the second.
                 auto issue_pv_half = [&](int t, uint32_t v_addr, bool acc, int half) {
                     const uint64_t dv0 = smem_desc_sw128(v_addr, SUB, 1024);
 #pragma unroll
@@ -424,151 +597,174 @@ fa_mask_fwd_kernel(const __grid_constant__ CUtensorMap tm_q,
                                (acc || ks > 0) ? 1u : 0u);
                     }
                 };
-
-                // waits for the two halves of P of step j in turn and issues their MMAs
-                auto issue_pv = [&](int t, uint32_t v_addr, int j) -> bool {
-                    if (!mbar_wait(bar_p_ready + 8 * t, j & 1, abort_flag, p.status, kStMmaP)) return false;
+                // waits for the two halves of P of the slot's next step and issues their MMAs;
+                // `first` = first step of the unit (O is overwritten, not accumulated)
+                auto issue_pv = [&](int t, uint32_t v_addr, bool first) -> bool {
+                    if (!mbar_wait(bar_p_ready + 8 * t, p_phase[t], abort_flag, p.status, kStMmaP)) return false;
                     tc_fence_after();
-                    issue_pv_half(t, v_addr, j > 0, 0);
-                    if (!mbar_wait(bar_p_ready2 + 8 * t, j & 1, abort_flag, p.status, kStMmaP)) return false;
+                    issue_pv_half(t, v_addr, !first, 0);
+                    if (!mbar_wait(bar_p_ready2 + 8 * t, p_phase[t], abort_flag, p.status, kStMmaP)) return false;
                     tc_fence_after();
                     issue_pv_half(t, v_addr, true, 1);
+                    p_phase[t] ^= 1u;
                     return true;
                 };
+                auto wait_tile = [&](const Ring& r) -> bool {
+                    return mbar_wait(bar_kv_full + 8 * r.slot, r.phase, abort_flag, p.status, kStMmaKv);
+                };
 
-                bool ok = (n > 0) && mbar_wait(bar_q_full, 0, abort_flag, p.status, kStMmaQ);
-                if (dual) {
-                    // Two independent streams; every K/V tile belongs to one slot and is
-                    // released as soon as that slot's MMAs are issued.  `f` walks the ring in
-                    // the producer's order.
-                    int f = 0;
-                    auto take = [&](uint32_t& addr) -> bool {
-                        const int slot = f % ring_slots;
-                        const bool got = mbar_wait(bar_kv_full + 8 * slot, (f / ring_slots) & 1,
-                                                   abort_flag, p.status, kStMmaKv);
-                        addr = ring_base + slot * TILE;
-                        return got;
-                    };
-                    auto release = [&]() {
-                        mma_commit(bar_kv_empty + 8 * (f % ring_slots));
-                        ++f;
-                    };
-                    uint32_t addr = 0;
-#pragma unroll
-                    for (int t = 0; t < 2; ++t) {
-                        if (ok && sl_n[t] > 0 && (ok = take(addr))) {
-                            tc_fence_after();
-                            issue_s(t, addr);
-                            mma_commit(bar_s_full + 8 * t);
-                            release();
-                        }
-                    }
-                    for (int j = 0; ok && j < nmax; ++j) {
+                int k = 0;
+                for (; ok; ++k) {
+                    const uint32_t ui = unit_wait(k);
+                    if (!(ok = (ui != 0u)) || ui_get(ui, kUiUnit) < 0) break;
+                    const int n0 = max(ui_get(ui, kUiSlot + kUiN), 0);
+                    const int n1 = max(ui_get(ui, kUiSlot + 4 + kUiN), 0);
+                    unit_done(k);                // only the counts are needed here
+                    if (n0 <= 0) continue;
+                    if (!(ok = mbar_wait(bar_q_full, q_phase[0], abort_flag, p.status, kStMmaQ))) break;
+                    q_phase[0] ^= 1u;
+                    if (dual) {
+                        // Two independent streams over a ring of NS + 1 slots; every K/V tile
+                        // belongs to one slot and is released as soon as that slot's MMAs are
+                        // issued.
+                        const int n_of[2] = {n0, n1};
+                        const int nmax = max(n0, n1);
+                        auto release = [&]() {
+                            mma_commit(bar_kv_empty + 8 * ring.slot);
+                            ring.advance(NS + 1);
+                        };
 #pragma unroll
                         for (int t = 0; t < 2; ++t) {
-                            if (!ok || j >= sl_n[t]) continue;
-                            if (!(ok = take(addr))) break;                       // V_t(j)
-                            if (!(ok = issue_pv(t, addr, j))) break;
-                            release();
-                            if (j + 1 < sl_n[t]) {
-                                if (!(ok = take(addr))) break;                   // K_t(j+1)
+                            if (ok && n_of[t] > 0 && (ok = wait_tile(ring))) {
                                 tc_fence_after();
-                                issue_s(t, addr);
+                                issue_s(t, ring_base + ring.slot * TILE);
                                 mma_commit(bar_s_full + 8 * t);
                                 release();
-                            } else {
-                                mma_commit(bar_o_full + 8 * t);
                             }
                         }
+                        for (int j = 0; ok && j < nmax; ++j) {
+#pragma unroll
+                            for (int t = 0; t < 2; ++t) {
+                                if (!ok || j >= n_of[t]) continue;
+                                if (!(ok = wait_tile(ring))) continue;                    // V_t(j)
+                                if (!(ok = issue_pv(t, ring_base + ring.slot * TILE, j == 0))) continue;
+                                release();
+                                if (j + 1 < n_of[t]) {
+                                    if (!(ok = wait_tile(ring))) continue;                // K_t(j+1)
+                                    tc_fence_after();
+                                    issue_s(t, ring_base + ring.slot * TILE);
+                                    mma_commit(bar_s_full + 8 * t);
+                                    release();
+                                } else {
+                                    mma_commit(bar_o_full + 8 * t);
+                                }
+                            }
+                        }
+                        continue;
                     }
-                    ok = false;                                                  // pair path below is skipped
-                }
-                ok = ok && mbar_wait(bar_kv_full, 0, abort_flag, p.status, kStMmaKv);
-                if (ok) {
+                    // ---- pair mode: K_j and V_j are shared by the two query tiles
+                    const bool has_q1 = n1 > 0;
+                    if (!(ok = wait_tile(ring))) break;                                   // K_0
                     tc_fence_after();
-                    issue_s(0, sKV);
+                    issue_s(0, sKV + ring.slot * TILE);
                     mma_commit(bar_s_full);
+                    if (n0 == 1) mma_commit(bar_q_free);          // that was tile 0's last S
                     if (has_q1) {
-                        ok = mbar_wait(bar_q_full + 8, 0, abort_flag, p.status, kStMmaQ);
-                        if (ok) {
-                            tc_fence_after();
-                            issue_s(1, sKV);
-                            mma_commit(bar_s_full + 8);
-                        }
-                    }
-                    mma_commit(bar_kv_empty);           // K_0's slot
-                }
-                for (int j = 0; ok && j < n; ++j) {
-                    const int fv = 2 * j + 1;
-                    const int fk = 2 * j + 2;
-                    const bool more = (j + 1) < n;
-                    const uint32_t v_addr = sKV + (fv % NS) * TILE;
-                    const uint32_t k_addr = sKV + (fk % NS) * TILE;
-                    if (!(ok = mbar_wait(bar_kv_full + 8 * (fv % NS), (fv / NS) & 1, abort_flag,
-                                         p.status, kStMmaKv)))
-                        break;
-                    // ---- tile 0
-                    if (!(ok = issue_pv(0, v_addr, j))) break;
-                    if (more) {
-                        if (!(ok = mbar_wait(bar_kv_full + 8 * (fk % NS), (fk / NS) & 1, abort_flag,
-                                             p.status, kStMmaKv)))
-                            break;
+                        if (!(ok = mbar_wait(bar_q_full + 8, q_phase[1], abort_flag, p.status, kStMmaQ))) break;
+                        q_phase[1] ^= 1u;
                         tc_fence_after();
-                        issue_s(0, k_addr);
-                        mma_commit(bar_s_full);
-                    } else {
-                        mma_commit(bar_o_full);
+                        issue_s(1, sKV + ring.slot * TILE);
+                        mma_commit(bar_s_full + 8);
+                        if (n0 == 1) mma_commit(bar_q_free + 8);
                     }
-                    // ---- tile 1
-                    if (has_q1) {
-                        if (!(ok = issue_pv(1, v_addr, j))) break;
-                        mma_commit(bar_kv_empty + 8 * (fv % NS));
+                    mma_commit(bar_kv_empty + 8 * ring.slot);
+                    ring.advance(NS);
+                    for (int j = 0; ok && j < n0; ++j) {
+                        const bool more = (j + 1) < n0;
+                        const bool last_s = (j + 2) == n0;        // the S issued in this step is the unit's last
+                        const Ring rv = ring;                     // V_j
+                        Ring rk = ring;                           // K_{j+1}
+                        rk.advance(NS);
+                        const uint32_t v_addr = sKV + rv.slot * TILE;
+                        const uint32_t k_addr = sKV + rk.slot * TILE;
+                        if (!(ok = wait_tile(rv))) break;
+                        // ---- tile 0
+                        if (!(ok = issue_pv(0, v_addr, j == 0))) break;
                         if (more) {
-                            issue_s(1, k_addr);
-                            mma_commit(bar_s_full + 8);
-                            mma_commit(bar_kv_empty + 8 * (fk % NS));
+                            if (!(ok = wait_tile(rk))) break;
+                            tc_fence_after();
+                            issue_s(0, k_addr);
+                            mma_commit(bar_s_full);
+                            if (last_s) mma_commit(bar_q_free);
                         } else {
-                            mma_commit(bar_o_full + 8);
+                            mma_commit(bar_o_full);
                         }
-                    } else {
-                        mma_commit(bar_kv_empty + 8 * (fv % NS));
-                        if (more) mma_commit(bar_kv_empty + 8 * (fk % NS));
+                        // ---- tile 1
+                        if (has_q1) {
+                            if (!(ok = issue_pv(1, v_addr, j == 0))) break;
+                            mma_commit(bar_kv_empty + 8 * rv.slot);
+                            if (more) {
+                                issue_s(1, k_addr);
+                                mma_commit(bar_s_full + 8);
+                                if (last_s) mma_commit(bar_q_free + 8);
+                                mma_commit(bar_kv_empty + 8 * rk.slot);
+                            } else {
+                                mma_commit(bar_o_full + 8);
+                            }
+                        } else {
+                            mma_commit(bar_kv_empty + 8 * rv.slot);
+                            if (more) mma_commit(bar_kv_empty + 8 * rk.slot);
+                        }
+                        ring = rk;
+                        if (more) ring.advance(NS);
                     }
                 }
             }
         }
     } else {
         reg_alloc<kSoftmaxRegs>();
-        if (sl_on[warp >> 2]) {
-            // -------------------------------------------------------------- softmax groups
-            const int t = warp >> 2;
-            const int wq = warp & 3;
-            const int row_in_tile = wq * 32 + lane;
-            const int row = sl_row0[t] + row_in_tile;
-            const int n_t = sl_n[t];
-            const int split = sl_split[t];
-            const bool row_ok = row < p.Sq;
-            const uint32_t lane_sel = static_cast<uint32_t>(wq * 32) << 16;
-            const uint32_t tS = tmem_base + lane_sel + t * 128;
-            const uint32_t tO = tmem_base + lane_sel + 256 + t * 128;
-            const uint32_t bar_s = bar_s_full + 8 * t;
-            const uint32_t bar_p = bar_p_ready + 8 * t;
-            const uint32_t bar_p2 = bar_p_ready2 + 8 * t;
-            // this thread's row inside a swizzled mask panel: 16-byte chunk c of row r
-            // lives at r*128 + ((c ^ (r & 7)) << 4)
-            const uint32_t m_row_addr = sM + (2 * t) * kPanelBytes + row_in_tile * 128;
-            const uint32_t m_xor = static_cast<uint32_t>(row_in_tile & 7) << 4;
-            const float2 scale2 = make_float2(p.scale, p.scale);
+        // ------------------------------------------------------------------ softmax groups
+        const int t = warp >> 2;
+        const int wq = warp & 3;
+        const int row_in_tile = wq * 32 + lane;
+        const uint32_t lane_sel = static_cast<uint32_t>(wq * 32) << 16;
+        const uint32_t tS = tmem_base + lane_sel + t * 128;
+        const uint32_t tO = tmem_base + lane_sel + 256 + t * 128;
+        const uint32_t bar_s = bar_s_full + 8 * t;
+        const uint32_t bar_p = bar_p_ready + 8 * t;
+        const uint32_t bar_p2 = bar_p_ready2 + 8 * t;
+        // this thread's row inside a swizzled mask panel: 16-byte chunk c of row r
+        // lives at r*128 + ((c ^ (r & 7)) << 4)
+        const uint32_t m_row_addr = sM + (2 * t) * kPanelBytes + row_in_tile * 128;
+        const uint32_t m_xor = static_cast<uint32_t>(row_in_tile & 7) << 4;
+        const float2 scale2 = make_float2(p.scale, p.scale);
+
+        int gstep = 0;               // key-block steps of this slot so far, over all units
+        int o_uses = 0;              // units of this slot that waited for their final O
+        bool alive = true;
+        int k = 0;
+        for (; alive; ++k) {
+            const uint32_t ui = unit_wait(k);
+            if (!__all_sync(0xffffffffu, ui != 0u)) { alive = false; break; }
+            if (ui_get(ui, kUiUnit) < 0) break;
+            const uint32_t lst = blk_list + (k & 1) * (kMaxListBlocks * 2);
+            const int n_t = ui_get(ui, kUiSlot + 4 * t + kUiN);
+            if (n_t < 0) {                           // the slot does not exist in this unit
+                __syncwarp();
+                if (lane == 0) unit_done(k);
+                continue;
+            }
+            const int begin_t = ui_get(ui, kUiSlot + 4 * t + kUiBegin);
 
             float m_ref = -INFINITY;     // reference maximum of the scaled, masked scores
             float l = 0.f;               // row sum relative to m_ref
-            bool alive = true;
 
-            for (int j = 0; j < n_t; ++j) {
-                const int col0 = blk(t, j) * kBlockN;
+            for (int j = 0; j < n_t; ++j, ++gstep) {
+                const int col0 = (LIST ? static_cast<int>(lds16(lst + 2 * j)) : begin_t + j) * kBlockN;
                 const bool tail = (col0 + kBlockN) > p.Sk;
+                const uint32_t par = gstep & 1;
 
-                bool ok = mbar_wait(bar_s, j & 1, abort_flag, p.status, kStSoftmaxS);
+                bool ok = mbar_wait(bar_s, par, abort_flag, p.status, kStSoftmaxS);
                 if (!__all_sync(0xffffffffu, ok)) { alive = false; break; }
                 tc_fence_after();
 
@@ -579,7 +775,7 @@ fa_mask_fwd_kernel(const __grid_constant__ CUtensorMap tm_q,
                 float mt0 = -INFINITY, mt1 = -INFINITY;
 #pragma unroll
                 for (int pn = 0; pn < 2; ++pn) {
-                    ok = mbar_wait(bar_m_full + 8 * (2 * t + pn), j & 1, abort_flag, p.status,
+                    ok = mbar_wait(bar_m_full + 8 * (2 * t + pn), par, abort_flag, p.status,
                                    kStSoftmaxMask);
                     if (!__all_sync(0xffffffffu, ok)) { alive = false; break; }
 #pragma unroll
@@ -676,81 +872,92 @@ fa_mask_fwd_kernel(const __grid_constant__ CUtensorMap tm_q,
                 tc_fence_before();
                 mbar_arrive(bar_p2);
             }
+            if (!alive) break;
+            // the rest of the unit's description is read from the board only now, so that it
+            // holds no registers during the loop above
+            const int row = ui_get(ui, kUiSlot + 4 * t + kUiRow0) + row_in_tile;
+            const bool row_ok = row < p.Sq;
+            const int u_b = ui_get(ui, kUiB), u_h = ui_get(ui, kUiH), u_sgroup = ui_get(ui, kUiSgroup);
+            const int split_t = ui_get(ui, kUiSlot + 4 * t + kUiSplit);
+            const int n_other = ui_get(ui, kUiSlot + 4 * (t ^ 1) + kUiN);
+            __syncwarp();
+            if (lane == 0) unit_done(k);          // this warp no longer reads the board or the list
 
             // ---- epilogue: O / l, to the output dtype (or fp32 partial + LSE when split)
             // (a slot whose every key block was skipped has nothing in tensor memory: its rows
             // are fully masked, the result is 0 and the LSE -inf)
             const bool empty = (n_t == 0);
-            if (alive && !empty) {
-                bool ok = mbar_wait(bar_o_full + 8 * t, 0, abort_flag, p.status, kStSoftmaxO);
-                alive = __all_sync(0xffffffffu, ok);
+            if (!empty) {
+                bool ok = mbar_wait(bar_o_full + 8 * t, o_uses & 1, abort_flag, p.status, kStSoftmaxO);
+                ++o_uses;
+                if (!__all_sync(0xffffffffu, ok)) { alive = false; break; }
             }
-            const bool merge_slots = dual && sl_n[0] > 0 && sl_n[1] > 0;
-            if (alive && merge_slots) {
+            const bool merge_slots = dual && n_t > 0 && n_other > 0;
+            if (merge_slots) {
                 // Dual mode: the two slots hold partial results of the SAME rows over two key
                 // ranges.  They are merged here, in the CTA, so one partial goes to memory
                 // instead of two: each group publishes (max, sum) of its rows in its own, now
                 // idle, mask panel, reads the other group's, and normalises half of the
-                // columns of  a0*O0 + a1*O1  straight out of tensor memory.
+                // columns of  a0*O0 + a1*O1  straight out of tensor memory.  (Dual mode runs
+                // one unit per CTA, so the panel and the barrier are used once.)
                 const uint32_t own = sM + (2 * t) * kPanelBytes + row_in_tile * 8;
                 const uint32_t other = sM + (2 * (t ^ 1)) * kPanelBytes + row_in_tile * 8;
                 sts32(own, __float_as_uint(m_ref));
                 sts32(own + 4, __float_as_uint(l));
                 mbar_arrive(bar_merge);
                 bool ok = mbar_wait(bar_merge, 0, abort_flag, p.status, kStSoftmaxO);
-                alive = __all_sync(0xffffffffu, ok);
-                if (alive) {
-                    tc_fence_after();
-                    const float m_o = __uint_as_float(lds32(other));
-                    const float l_o = __uint_as_float(lds32(other + 4));
-                    const bool dead_s = (m_ref == -INFINITY) || !(l > 0.f);
-                    const bool dead_o = (m_o == -INFINITY) || !(l_o > 0.f);
-                    const float m_all = fmaxf(dead_s ? -INFINITY : m_ref, dead_o ? -INFINITY : m_o);
-                    const float a_s = dead_s ? 0.f : __expf(m_ref - m_all);
-                    const float a_o = dead_o ? 0.f : __expf(m_o - m_all);
-                    const float l_all = a_s * l + a_o * l_o;
-                    const bool dead = dead_s && dead_o;
-                    const float inv = dead ? 0.f : 1.f / l_all;
-                    const float w_s = a_s * inv, w_o = a_o * inv;
-                    const long long prow =
-                        ((static_cast<long long>(sgroup) * p.B + b) * p.H + h) * p.Sq + row;
-                    if (row_ok && t == 0) p.lse_part[prow] = dead ? -INFINITY : m_all + __logf(l_all);
-                    float* dst = p.o_part + prow * D;
-                    const uint32_t tO_other = tmem_base + lane_sel + 256 + (t ^ 1) * 128;
-                    constexpr int kChunks = D / 32;
+                if (!__all_sync(0xffffffffu, ok)) { alive = false; break; }
+                tc_fence_after();
+                const float m_o = __uint_as_float(lds32(other));
+                const float l_o = __uint_as_float(lds32(other + 4));
+                const bool dead_s = (m_ref == -INFINITY) || !(l > 0.f);
+                const bool dead_o = (m_o == -INFINITY) || !(l_o > 0.f);
+                const float m_all = fmaxf(dead_s ? -INFINITY : m_ref, dead_o ? -INFINITY : m_o);
+                const float a_s = dead_s ? 0.f : __expf(m_ref - m_all);
+                const float a_o = dead_o ? 0.f : __expf(m_o - m_all);
+                const float l_all = a_s * l + a_o * l_o;
+                const bool dead = dead_s && dead_o;
+                const float inv = dead ? 0.f : 1.f / l_all;
+                const float w_s = a_s * inv, w_o = a_o * inv;
+                const long long prow =
+                    ((static_cast<long long>(u_sgroup) * p.B + u_b) * p.H + u_h) * p.Sq + row;
+                if (row_ok && t == 0) p.lse_part[prow] = dead ? -INFINITY : m_all + __logf(l_all);
+                float* dst = p.o_part + prow * D;
+                const uint32_t tO_other = tmem_base + lane_sel + 256 + (t ^ 1) * 128;
+                constexpr int kChunks = D / 32;
 #pragma unroll
-                    for (int cc = 0; cc < kChunks / 2; ++cc) {
-                        const int c = t * (kChunks / 2) + cc;          // this group's half of the columns
-                        uint32_t os[32], oo[32];
-                        tmem_ld32(tO + c * 32, os);
-                        tmem_ld32(tO_other + c * 32, oo);
-                        if (row_ok) {
+                for (int cc = 0; cc < kChunks / 2; ++cc) {
+                    const int c = t * (kChunks / 2) + cc;          // this group's half of the columns
+                    uint32_t os[32], oo[32];
+                    tmem_ld32(tO + c * 32, os);
+                    tmem_ld32(tO_other + c * 32, oo);
+                    if (row_ok) {
 #pragma unroll
-                            for (int i = 0; i < 32; i += 4) {
-                                float4 f;
-                                f.x = __uint_as_float(os[i]) * w_s + __uint_as_float(oo[i]) * w_o;
-                                f.y = __uint_as_float(os[i + 1]) * w_s + __uint_as_float(oo[i + 1]) * w_o;
-                                f.z = __uint_as_float(os[i + 2]) * w_s + __uint_as_float(oo[i + 2]) * w_o;
-                                f.w = __uint_as_float(os[i + 3]) * w_s + __uint_as_float(oo[i + 3]) * w_o;
-                                *reinterpret_cast<float4*>(dst + c * 32 + i) = f;
-                            }
+                        for (int i = 0; i < 32; i += 4) {
+                            float4 f;
+                            f.x = __uint_as_float(os[i]) * w_s + __uint_as_float(oo[i]) * w_o;
+                            f.y = __uint_as_float(os[i + 1]) * w_s + __uint_as_float(oo[i + 1]) * w_o;
+                            f.z = __uint_as_float(os[i + 2]) * w_s + __uint_as_float(oo[i + 2]) * w_o;
+                            f.w = __uint_as_float(os[i + 3]) * w_s + __uint_as_float(oo[i + 3]) * w_o;
+                            *reinterpret_cast<float4*>(dst + c * 32 + i) = f;
                         }
                     }
                 }
-            } else if (alive) {
+            } else {
                 tc_fence_after();
                 // A row that never saw a visible key still has the reference maximum -inf; its
                 // sum and accumulator hold only rounding dust of the polynomial exponential.
                 const bool dead = (m_ref == -INFINITY) || !(l > 0.f);
                 const float inv = dead ? 0.f : (1.f / l);
                 const float lse_val = dead ? -INFINITY : m_ref + __logf(l);
-                const long long grow = (static_cast<long long>(b) * p.H + h) * p.Sq + row;
+                const long long grow = (static_cast<long long>(u_b) * p.H + u_h) * p.Sq + row;
                 const bool split_out = p.num_splits > 1;
                 float* o32 = nullptr;
                 if (split_out) {
                     // dual mode stores one partial per CTA (split group), otherwise one per split
                     const long long prow =
-                        ((static_cast<long long>(dual ? sgroup : split) * p.B + b) * p.H + h) * p.Sq + row;
+                        ((static_cast<long long>(dual ? u_sgroup : split_t) * p.B + u_b) * p.H + u_h) *
+                            p.Sq + row;
                     o32 = p.o_part + prow * D;
                     if (row_ok) p.lse_part[prow] = lse_val;
                 } else {
@@ -758,39 +965,79 @@ fa_mask_fwd_kernel(const __grid_constant__ CUtensorMap tm_q,
                     if (row_ok && p.lse != nullptr) p.lse[grow] = lse_val;
                 }
                 uint16_t* o16 = static_cast<uint16_t*>(p.out) + grow * D;
-#pragma unroll
-                for (int c = 0; c < D / 32; ++c) {
-                    uint32_t o[32];
+                if (p.wide_stores) {
+                    // quad-transposed, line-sized stores (see quad_transpose); the whole row is
+                    // read from tensor memory with one load and one wait
+                    const int rows_left = p.Sq - row;
+                    uint32_t o[D];
                     if (!empty) {
-                        tmem_ld32(tO + c * 32, o);
+                        if constexpr (D == 128) tmem_ld128(tO, o);
+                        else tmem_ld64(tO, o);
                     } else {
 #pragma unroll
-                        for (int i = 0; i < 32; ++i) o[i] = 0u;
+                        for (int i = 0; i < D; ++i) o[i] = 0u;
                     }
-                    if (row_ok) {
-                        if (o32 != nullptr) {
+                    if (o32 != nullptr) {
 #pragma unroll
-                            for (int i = 0; i < 32; i += 4) {
-                                float4 f;
-                                f.x = __uint_as_float(o[i]) * inv;
-                                f.y = __uint_as_float(o[i + 1]) * inv;
-                                f.z = __uint_as_float(o[i + 2]) * inv;
-                                f.w = __uint_as_float(o[i + 3]) * inv;
-                                *reinterpret_cast<float4*>(o32 + c * 32 + i) = f;
-                            }
+                        for (int c = 0; c < D / 32; ++c) {
+                            uint32_t w[32];
+#pragma unroll
+                            for (int i = 0; i < 32; ++i) w[i] = __float_as_uint(__uint_as_float(o[c * 32 + i]) * inv);
+                            quad_transpose(w, lane);
+                            quad_store(w, lane, reinterpret_cast<char*>(o32 + c * 32), static_cast<long long>(D) * 4,
+                                       rows_left);
+                        }
+                    } else {
+#pragma unroll
+                        for (int c = 0; c < D / 64; ++c) {
+                            uint32_t w[32];
+#pragma unroll
+                            for (int i = 0; i < 32; ++i)
+                                w[i] = pack2<BF16>(__uint_as_float(o[c * 64 + 2 * i]) * inv,
+                                                   __uint_as_float(o[c * 64 + 2 * i + 1]) * inv);
+                            quad_transpose(w, lane);
+                            quad_store(w, lane, reinterpret_cast<char*>(o16 + c * 64), static_cast<long long>(D) * 2,
+                                       rows_left);
+                        }
+                    }
+                } else {
+#pragma unroll
+                    for (int c = 0; c < D / 32; ++c) {
+                        uint32_t o[32];
+                        if (!empty) {
+                            tmem_ld32(tO + c * 32, o);
                         } else {
 #pragma unroll
-                            for (int i = 0; i < 32; i += 8) {
-                                uint4 u;
-                                u.x = pack2<BF16>(__uint_as_float(o[i]) * inv, __uint_as_float(o[i + 1]) * inv);
-                                u.y = pack2<BF16>(__uint_as_float(o[i + 2]) * inv, __uint_as_float(o[i + 3]) * inv);
-                                u.z = pack2<BF16>(__uint_as_float(o[i + 4]) * inv, __uint_as_float(o[i + 5]) * inv);
-                                u.w = pack2<BF16>(__uint_as_float(o[i + 6]) * inv, __uint_as_float(o[i + 7]) * inv);
-                                *reinterpret_cast<uint4*>(o16 + c * 32 + i) = u;
+                            for (int i = 0; i < 32; ++i) o[i] = 0u;
+                        }
+                        if (row_ok) {
+                            if (o32 != nullptr) {
+#pragma unroll
+                                for (int i = 0; i < 32; i += 4) {
+                                    float4 f;
+                                    f.x = __uint_as_float(o[i]) * inv;
+                                    f.y = __uint_as_float(o[i + 1]) * inv;
+                                    f.z = __uint_as_float(o[i + 2]) * inv;
+                                    f.w = __uint_as_float(o[i + 3]) * inv;
+                                    *reinterpret_cast<float4*>(o32 + c * 32 + i) = f;
+                                }
+                            } else {
+#pragma unroll
+                                for (int i = 0; i < 32; i += 8) {
+                                    uint4 uu;
+                                    uu.x = pack2<BF16>(__uint_as_float(o[i]) * inv, __uint_as_float(o[i + 1]) * inv);
+                                    uu.y = pack2<BF16>(__uint_as_float(o[i + 2]) * inv, __uint_as_float(o[i + 3]) * inv);
+                                    uu.z = pack2<BF16>(__uint_as_float(o[i + 4]) * inv, __uint_as_float(o[i + 5]) * inv);
+                                    uu.w = pack2<BF16>(__uint_as_float(o[i + 6]) * inv, __uint_as_float(o[i + 7]) * inv);
+                                    *reinterpret_cast<uint4*>(o16 + c * 32 + i) = uu;
+                                }
                             }
                         }
                     }
                 }
+                // the next unit's first P.V overwrites O: every read above has completed
+                // (tcgen05.wait::ld inside the loads), order it before the next arrivals
+                tc_fence_before();
             }
         }
     }
@@ -919,10 +1166,13 @@ __device__ unsigned int g_skip_ticket = 0;
 
 __global__ void __launch_bounds__(256)
 fa_mask_classify_kernel(const uint16_t* __restrict__ mask, long long bs, long long rs, int Sq, int Sk,
-                        uint32_t neg_inf2, unsigned char* __restrict__ flags, int* hint) {
+                        uint32_t neg_inf2, unsigned char* __restrict__ flags, int* hint,
+                        unsigned int* unit_counter) {
     const int nt = blockIdx.x, mp = blockIdx.y, b = blockIdx.z;
     pdl_wait_prior_grid();                          // a re-pitch kernel may have written the mask
     pdl_launch_dependents();
+    // the attention kernel behind this one hands out its units from this counter
+    if ((blockIdx.x | blockIdx.y | blockIdx.z | threadIdx.x) == 0) *unit_counter = 0u;
     const int vec = threadIdx.x & 15;               // 16 vectors of 8 keys per 128-key row piece
     const int rsub = threadIdx.x >> 4;              // 16 rows per pass
     const int col = nt * kBlockN + vec * 8;
@@ -1126,12 +1376,14 @@ static int make_plan(const FaMaskFwdArgs* a, FaMaskFwdPlan* plan) {
     plan->kv_blocks = nb;
     plan->blocks_per_split = bps;
     plan->q_tiles_per_cta = a->seqlen_q > kBlockM ? 2 : 1;
-    // One CTA per unit of (split, 256-row query pair, head, batch).  Splitting the units of a
+    // Units of (split, 256-row query pair, head, batch).  Pair mode is persistent: one CTA per
+    // SM takes every grid_x-th unit, so the loads and the first MMA of a unit run under the
+    // previous unit's epilogue.  Dual mode runs one unit per CTA.  (Splitting the units of a
     // half-empty last round into single-tile CTAs was measured and gains nothing: a CTA's time
-    // is set by the per-tile softmax -> MMA dependency chain, not by how many tiles it holds.
+    // is set by the per-tile softmax -> MMA dependency chain, not by how many tiles it holds.)
     const long long units = static_cast<long long>(m_pairs) * split_groups * a->heads * a->batch;
     if (units > 0x3fffffffLL) return FA_SM100_ERR_SHAPE;
-    plan->grid_x = static_cast<int32_t>(units);
+    plan->grid_x = static_cast<int32_t>((dual || units < dev->sm_count) ? units : dev->sm_count);
     plan->grid_y = 1;
     plan->grid_z = 1;
     plan->dual_split = dual ? 1 : 0;
@@ -1153,7 +1405,8 @@ static int make_plan(const FaMaskFwdArgs* a, FaMaskFwdPlan* plan) {
     // Tile skipping: single pass over the keys, at least two key blocks, list fits the CTA.
     plan->tile_skip = (splits == 1 && nb >= 4 && nb <= kMaxListBlocks && a->seqlen_q > 0 &&
                        a->no_tile_skip == 0) ? 1 : 0;
-    if (plan->tile_skip) ws += align256(static_cast<size_t>(a->batch) * m_pairs * nb);
+    // (block flags, then the counter the attention kernel hands out its units from)
+    if (plan->tile_skip) ws += align256(static_cast<size_t>(a->batch) * m_pairs * nb) + 256;
     plan->workspace_bytes = ws;
     return FA_SM100_OK;
 }
@@ -1498,6 +1751,8 @@ static int forward(const FaMaskFwdArgs* a, void* workspace, size_t workspace_byt
     if (run_classify) {
         unsigned char* flags = ws + (plan.mask_repitched
             ? align256(static_cast<size_t>(a->batch) * a->seqlen_q * ((a->seqlen_k + 7) & ~7) * 2) : 0);
+        unsigned int* unit_counter = reinterpret_cast<unsigned int*>(
+            flags + align256(static_cast<size_t>(a->batch) * ceil_div(a->seqlen_q, 2 * kBlockM) * plan.kv_blocks));
         const dim3 cgrid(plan.kv_blocks, ceil_div(a->seqlen_q, 2 * kBlockM), a->batch);
         const uint32_t ninf = a->dtype == FA_SM100_BF16 ? 0xFF80FF80u : 0xFC00FC00u;
         cudaLaunchConfig_t cfg = {};
@@ -1510,11 +1765,12 @@ static int forward(const FaMaskFwdArgs* a, void* workspace, size_t workspace_byt
         cfg.attrs = attr;
         cfg.numAttrs = plan.mask_repitched ? 1 : 0;      // chained behind the re-pitch kernel
         if (cudaLaunchKernelEx(&cfg, fa_mask_classify_kernel, mask_ptr, mask_bs, mask_rs, a->seqlen_q,
-                               a->seqlen_k, ninf, flags, hint_counter) != cudaSuccess) {
+                               a->seqlen_k, ninf, flags, hint_counter, unit_counter) != cudaSuccess) {
             return cuda_failed(__LINE__);
         }
         ++g_launches;
         kp.block_flags = flags;
+        kp.unit_counter = unit_counter;
     }
     kp.out = a->out;
     kp.lse = a->lse;
@@ -1527,7 +1783,9 @@ static int forward(const FaMaskFwdArgs* a, void* workspace, size_t workspace_byt
     kp.m_pairs = ceil_div(a->seqlen_q, 2 * kBlockM);
     kp.dual = plan.dual_split;
     kp.split_groups = plan.dual_split ? ceil_div(plan.num_splits, 2) : plan.num_splits;
+    kp.total_units = kp.m_pairs * kp.split_groups * a->heads * a->batch;
     kp.out_fp32 = a->out_fp32;
+    kp.wide_stores = (((reinterpret_cast<uintptr_t>(a->out) | reinterpret_cast<uintptr_t>(o_part)) & 31u) == 0) ? 1 : 0;
     kp.scale = static_cast<float>(1.0 / std::sqrt(static_cast<double>(d)));
 
     CUtensorMap tq, tk, tv, tm;

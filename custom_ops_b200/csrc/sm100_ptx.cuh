@@ -71,21 +71,23 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 constexpr long long kMaxWaitCycles = 200000000LL;
 constexpr uint32_t kMaxPolls = 1u << 16;     // cap for the drain loops that have no clock check
 
-// Bounded wait.  `abort_flag` is a CTA-shared word: once any role of the CTA gave
-// up, every other wait of that CTA returns at once so the CTA drains and exits.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity,
-                                          volatile uint32_t* abort_flag,
+// Bounded wait.  `abort_saddr` is the shared-space address of a CTA-shared word: once any
+// role of the CTA gave up, every other wait of that CTA returns at once so the CTA drains
+// and exits.  (A shared-space address costs one register where a generic pointer costs two.)
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, uint32_t abort_saddr,
                                           unsigned int* status, uint32_t code) {
     if (mbar_try_wait(bar, parity)) return true;
     const long long t0 = clock64();
     for (uint32_t i = 0;; ++i) {
         if (mbar_try_wait(bar, parity)) return true;
         if ((i & 31u) == 31u) {
-            if (*abort_flag) return false;
+            uint32_t gave_up;
+            asm volatile("ld.volatile.shared.u32 %0, [%1];" : "=r"(gave_up) : "r"(abort_saddr) : "memory");
+            if (gave_up) return false;
             if (clock64() - t0 > kMaxWaitCycles) break;
         }
     }
-    *abort_flag = 1;
+    asm volatile("st.volatile.shared.u32 [%0], %1;" ::"r"(abort_saddr), "r"(1u) : "memory");
     atomicMax(status, code);
     return false;
 }
@@ -219,6 +221,23 @@ __device__ __forceinline__ uint32_t lds32(uint32_t saddr) {
     uint32_t v;
     asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(saddr) : "memory");
     return v;
+}
+
+// 256-bit store to global memory (32-byte aligned address).
+__device__ __forceinline__ void stg256(void* gptr, const uint32_t* r) {
+    asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(gptr), "r"(r[0]), "r"(r[1]),
+                 "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7])
+                 : "memory");
+}
+
+__device__ __forceinline__ uint32_t lds16(uint32_t saddr) {
+    uint16_t v;
+    asm volatile("ld.shared.u16 %0, [%1];" : "=h"(v) : "r"(saddr) : "memory");
+    return v;
+}
+
+__device__ __forceinline__ void sts16(uint32_t saddr, uint32_t v) {
+    asm volatile("st.shared.u16 [%0], %1;" ::"r"(saddr), "h"(static_cast<uint16_t>(v)) : "memory");
 }
 
 __device__ __forceinline__ void sts32(uint32_t saddr, uint32_t v) {

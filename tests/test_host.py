@@ -48,8 +48,10 @@ def _plan(**kw):
 def test_plan_of_the_five_configurations():
     sm = _plan().sm_count                      # 148 where no device can be queried
     p = _plan(batch=4, heads=16, heads_k=16, seqlen_q=2048, seqlen_k=2048)
-    assert (p.num_splits, p.kv_blocks, p.grid_x, p.q_tiles_per_cta) == (1, 16, 8 * 16 * 4, 2)
-    assert p.tile_skip == 1 and p.workspace_bytes == 512 and p.mask_repitched == 0 and p.threads == 384
+    # 8 * 16 * 4 = 512 units; pair mode is persistent: one CTA per SM takes every grid_x-th unit
+    assert (p.num_splits, p.kv_blocks, p.grid_x, p.q_tiles_per_cta) == (1, 16, min(512, sm), 2)
+    # block flags (4 * 8 * 16 bytes -> 512) + the unit counter
+    assert p.tile_skip == 1 and p.workspace_bytes == 512 + 256 and p.mask_repitched == 0 and p.threads == 384
     assert _plan(batch=4, heads=16, heads_k=16, seqlen_q=2048, seqlen_k=2048, no_tile_skip=1).workspace_bytes == 0
     p = _plan(batch=1, heads=16, heads_k=16, seqlen_q=128, seqlen_k=32768)
     assert p.kv_blocks == 256 and p.num_splits == 2 * max(1, sm // 16) and p.q_tiles_per_cta == 1
