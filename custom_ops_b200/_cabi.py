@@ -58,7 +58,7 @@ class FaMaskFwdArgs(ctypes.Structure):
         ("dtype", ctypes.c_int32),
         ("num_splits", ctypes.c_int32),
         ("out_fp32", ctypes.c_int32),
-        ("no_tile_skip", ctypes.c_int32),
+        ("disable", ctypes.c_int32),
     ]
 
 
@@ -77,7 +77,7 @@ class FaMaskFwdPlan(ctypes.Structure):
         ("sm_count", ctypes.c_int32),
         ("dual_split", ctypes.c_int32),
         ("tile_skip", ctypes.c_int32),
-        ("reserved", ctypes.c_int32),
+        ("unit_cut", ctypes.c_int32),
         ("workspace_bytes", ctypes.c_uint64),
     ]
 
@@ -145,10 +145,14 @@ def check(code: int):
         raise FaSm100Error(code, strerror(code))
 
 
+NO_TILE_SKIP = 1      # FaMaskFwdArgs.disable bits (FA_SM100_NO_*)
+NO_UNIT_CUT = 2
+
+
 def make_args(*, q=0, k=0, v=0, mask=0, out=0, lse=0, batch, heads, heads_k, seqlen_q, seqlen_k,
               head_dim, dtype, mask_seqlen_q=None, mask_seqlen_k=None, mask_batch_stride=None,
               mask_row_stride=None, device=0, num_splits=0, out_fp32=0,
-              no_tile_skip=0) -> FaMaskFwdArgs:
+              no_tile_skip=0, no_unit_cut=0) -> FaMaskFwdArgs:
     a = FaMaskFwdArgs()
     a.struct_size = ctypes.sizeof(FaMaskFwdArgs)
     a.device = device
@@ -164,7 +168,7 @@ def make_args(*, q=0, k=0, v=0, mask=0, out=0, lse=0, batch, heads, heads_k, seq
     a.dtype = dtype
     a.num_splits = num_splits
     a.out_fp32 = out_fp32
-    a.no_tile_skip = no_tile_skip
+    a.disable = (NO_TILE_SKIP if no_tile_skip else 0) | (NO_UNIT_CUT if no_unit_cut else 0)
     return a
 
 

@@ -52,6 +52,7 @@
 #include <cstdio>
 #include <cstdlib>
 #include <atomic>
+#include <chrono>
 #include <cstring>
 #include <mutex>
 
@@ -92,7 +93,7 @@ constexpr uint32_t kPanelBytes = 128 * 64 * 2;            // 128 rows x 64 colum
 // Status codes written to the device status word when a bounded wait runs out.
 enum : uint32_t {
     kStTmaEmpty = 1, kStMmaQ = 2, kStMmaKv = 3, kStMmaP = 4, kStSoftmaxS = 5, kStSoftmaxO = 6,
-    kStDrain = 7, kStMaskEmpty = 8, kStSoftmaxMask = 9, kStList = 10
+    kStDrain = 7, kStMaskEmpty = 8, kStSoftmaxMask = 9, kStList = 10, kStPartial = 11
 };
 
 __device__ unsigned int g_fa_status = 0;
@@ -126,6 +127,9 @@ struct KParams {
     unsigned int* unit_counter;         // with block_flags: units taken beyond the first of each CTA
     const unsigned char* block_flags;   // (B, m_pairs, kv_blocks): 0 = every key of the block is
                                         // masked (-inf) for all 256 rows -> skipped; NULL = no skipping
+    float* cut_part;          // per CTA: [256][D] fp32 O, then per CTA [256] LSE, then per CTA 8 tags
+    unsigned long long cut_tag;   // value a softmax warp stores in its tag once its partial is written
+    int cut_units;            // P >= 2: units of the last, partial round are done by P CTAs each; 0: whole
     int out_fp32;
     int wide_stores;          // 1: out and the partials are 32-byte aligned (256-bit stores)
     float scale;              // 1 / sqrt(d)
@@ -146,12 +150,23 @@ __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
     else return pack_f16x2(lo, hi);
 }
 
+// Unit cutting.  With G CTAs and units of equal length, whole rounds of G units go to the
+// CTAs one unit each; the R < G units of a last, partial round would leave most SMs idle, so
+// with P = G / R >= 2 each of them is done by P consecutive CTAs, one piece of its key blocks
+// each.  Every piece but the first (kPartTail) ends in a normalised fp32 partial plus LSE in
+// the CTA's slot of the workspace; the first piece (kPartHead) merges the partials of the
+// other pieces into its own result.  (Equal shares of ALL steps, or of the last round's, were
+// measured and lose: the partial traffic of 148 CTAs at once costs more than the idle SMs.)
+enum : int { kPartWhole = 0, kPartTail = 1, kPartHead = 2 };
+
 // Unit board: what the scheduler warp publishes about one unit of work, a (split group,
 // 256-row query pair, head, batch) combination, as ints in shared memory.  A CTA runs two
 // softmax/MMA streams ("slots"); words kUiSlot + 4 * t + ... describe slot t.
 enum : int {
     kUiB = 0, kUiH = 1, kUiSgroup = 2, kUiKvPlane = 3, kUiQPlane = 4,
     kUiUnit = 5,    // index of the unit; -1: no more work for this CTA
+    kUiPart = 6,    // kPartWhole, kPartTail or kPartHead
+    kUiPeerLast = 7,  // kPartHead: the last CTA that holds a piece of this unit
     kUiSlot = 8,
     kUiSplit = 0,   // KV split the slot covers
     kUiBegin = 1,   // first key block
@@ -485,12 +500,36 @@ fa_mask_fwd_kernel(const __grid_constant__ CUtensorMap tm_q,
             // gridDim.x-th one, or - with tile skipping, where units differ in length - the next
             // one nobody has taken yet, from a counter the pre-pass kernel reset.
             int unit = blockIdx.x;
+            // unit cutting (see kPartWhole): whole rounds first, then one piece of a unit of the
+            // last, partial round
+            const int whole_rounds = p.total_units / static_cast<int>(gridDim.x);
             for (int k = 0;; ++k) {
                 // board k&1 was last used by unit k-2: a fresh barrier passes at once
                 const bool ok = mbar_wait(bar_unit_empty + 8 * (k & 1), ((k >> 1) & 1) ^ 1u, abort_flag,
                                           p.status, kStList);
                 if (!__all_sync(0xffffffffu, ok)) break;
-                if (k > 0) {
+                int part = kPartWhole, part_begin = 0, part_n = p.kv_blocks, peer_last = 0;
+                if (!LIST && p.cut_units) {
+                    const int tail_unit = whole_rounds * static_cast<int>(gridDim.x) +
+                                          static_cast<int>(blockIdx.x) / p.cut_units;
+                    if (k < whole_rounds) {
+                        unit = static_cast<int>(blockIdx.x) + k * static_cast<int>(gridDim.x);
+                    } else if (k > whole_rounds || tail_unit >= p.total_units) {
+                        unit = p.total_units;
+                    } else {
+                        // CTAs c = u * P .. u * P + P - 1 share the u-th unit of the last round
+                        const int piece = static_cast<int>(blockIdx.x) % p.cut_units;
+                        unit = tail_unit;
+                        // The first piece is one key block longer than its share: the other
+                        // pieces' partials are then in memory by the time it wants them.
+                        const int shift = p.kv_blocks >= 2 * p.cut_units ? 1 : 0;
+                        part_begin = piece == 0 ? 0 : piece * p.kv_blocks / p.cut_units + shift;
+                        part_n = (piece + 1 == p.cut_units ? p.kv_blocks
+                                                           : (piece + 1) * p.kv_blocks / p.cut_units + shift) - part_begin;
+                        part = piece == 0 ? kPartHead : kPartTail;
+                        peer_last = static_cast<int>(blockIdx.x) + p.cut_units - 1;
+                    }
+                } else if (k > 0) {
                     if (LIST) {
                         if (lane == 0) unit = static_cast<int>(gridDim.x + atomicAdd(p.unit_counter, 1u));
                         unit = __shfl_sync(0xffffffffu, unit, 0);
@@ -535,8 +574,12 @@ fa_mask_fwd_kernel(const __grid_constant__ CUtensorMap tm_q,
                     // split s owns key blocks [s*nb/S, (s+1)*nb/S): sizes differ by at most one block
                     const unsigned nb = static_cast<unsigned>(p.kv_blocks), ns = static_cast<unsigned>(p.num_splits);
                     // (32 bits hold split * nb: at most 128 splits of at most 2^24 blocks)
-                    const int begin = static_cast<int>(static_cast<unsigned>(split) * nb / ns);
-                    const int end = static_cast<int>(static_cast<unsigned>(split + 1) * nb / ns);
+                    int begin = static_cast<int>(static_cast<unsigned>(split) * nb / ns);
+                    int end = static_cast<int>(static_cast<unsigned>(split + 1) * nb / ns);
+                    if (part != kPartWhole) {          // single pass, cut at a CTA boundary
+                        begin = part_begin;
+                        end = part_begin + part_n;
+                    }
                     const int row0 = dual ? m0 : m0 + t * kBlockM;
                     const bool on = dual ? (split < p.num_splits) : (row0 < p.Sq);
                     int n = on ? max(end - begin, 0) : -1;                 // -1: the slot does not exist
@@ -547,6 +590,8 @@ fa_mask_fwd_kernel(const __grid_constant__ CUtensorMap tm_q,
                     sts32(ui + 4 * (kUiSlot + 4 * t + kUiRow0), static_cast<uint32_t>(row0));
                     if (t == 0) {
                         sts32(ui + 4 * (kUiUnit), static_cast<uint32_t>(unit));
+                        sts32(ui + 4 * (kUiPart), static_cast<uint32_t>(part));
+                        sts32(ui + 4 * (kUiPeerLast), static_cast<uint32_t>(peer_last));
                         sts32(ui + 4 * (kUiB), static_cast<uint32_t>(b));
                         sts32(ui + 4 * (kUiH), static_cast<uint32_t>(h));
                         sts32(ui + 4 * (kUiSgroup), static_cast<uint32_t>(sgroup));
@@ -880,6 +925,8 @@ fa_mask_fwd_kernel(const __grid_constant__ CUtensorMap tm_q,
             const int u_b = ui_get(ui, kUiB), u_h = ui_get(ui, kUiH), u_sgroup = ui_get(ui, kUiSgroup);
             const int split_t = ui_get(ui, kUiSlot + 4 * t + kUiSplit);
             const int n_other = ui_get(ui, kUiSlot + 4 * (t ^ 1) + kUiN);
+            const int part = ui_get(ui, kUiPart);
+            const int peer_last = ui_get(ui, kUiPeerLast);
             __syncwarp();
             if (lane == 0) unit_done(k);          // this warp no longer reads the board or the list
 
@@ -948,12 +995,100 @@ fa_mask_fwd_kernel(const __grid_constant__ CUtensorMap tm_q,
                 // A row that never saw a visible key still has the reference maximum -inf; its
                 // sum and accumulator hold only rounding dust of the polynomial exponential.
                 const bool dead = (m_ref == -INFINITY) || !(l > 0.f);
-                const float inv = dead ? 0.f : (1.f / l);
-                const float lse_val = dead ? -INFINITY : m_ref + __logf(l);
+                float inv = dead ? 0.f : (1.f / l);
+                float lse_val = dead ? -INFINITY : m_ref + __logf(l);
+                const int tile_row = t * kBlockM + row_in_tile;        // row inside the 256-row pair
+                if (part == kPartHead) {
+                    // The other pieces of this unit were done by the next CTAs, up to peer_last:
+                    // in each, the softmax warp with the same rows wrote a normalised partial
+                    // and then its tag.
+                    const long long lse_base = static_cast<long long>(gridDim.x) * (2 * kBlockM) * D;
+                    const unsigned long long* tags = reinterpret_cast<const unsigned long long*>(
+                        p.cut_part + static_cast<long long>(gridDim.x) * (2 * kBlockM) * (D + 1));
+                    for (int slot = static_cast<int>(blockIdx.x) + 1; slot <= peer_last; ++slot) {
+                        bool ok = true;
+                        if (lane == 0) {
+                            const long long t0 = clock64();
+                            while (ld_acquire_u64(tags + slot * 8 + warp) != p.cut_tag) {
+                                if (lds32(abort_flag) != 0u || clock64() - t0 > kMaxWaitCycles) {
+                                    ok = false;
+                                    sts32(abort_flag, 1u);
+                                    atomicMax(p.status, static_cast<unsigned int>(kStPartial));
+                                    break;
+                                }
+                            }
+                        }
+                        if (!__all_sync(0xffffffffu, ok)) { alive = false; break; }
+                        const float* part_o = p.cut_part + (static_cast<long long>(slot) * (2 * kBlockM) + tile_row) * D;
+                        const float lse_p = ld_cg_f32(p.cut_part + lse_base + static_cast<long long>(slot) * (2 * kBlockM) +
+                                                      tile_row);
+                        // All loads of the partial are issued before the first is used (one at
+                        // a time they cost a trip to the L2 each).  The four lanes of a quad read
+                        // line-sized pieces of their four rows: the inverse of the stores below,
+                        // see quad_transpose.
+                        uint32_t pr[D];
+                        const int q4 = lane & 3;
+#pragma unroll
+                        for (int c = 0; c < D / 32; ++c) {
+#pragma unroll
+                            for (int i = 0; i < 4; ++i) {
+                                const float* src = part_o + (i - q4) * D + c * 32 + q4 * 8;
+                                const uint4 lo = ld_cg_v4(src), hi = ld_cg_v4(src + 4);
+                                pr[c * 32 + 8 * i] = lo.x; pr[c * 32 + 8 * i + 1] = lo.y;
+                                pr[c * 32 + 8 * i + 2] = lo.z; pr[c * 32 + 8 * i + 3] = lo.w;
+                                pr[c * 32 + 8 * i + 4] = hi.x; pr[c * 32 + 8 * i + 5] = hi.y;
+                                pr[c * 32 + 8 * i + 6] = hi.z; pr[c * 32 + 8 * i + 7] = hi.w;
+                            }
+                        }
+                        // out = (a_o * O/l + a_p * o_p) / (a_o + a_p),  a = exp(lse - max lse);
+                        // the merged, normalised row goes back to tensor memory
+                        const float mx = fmaxf(lse_val, lse_p);
+                        float w_o = 0.f, w_p = 0.f;
+                        if (mx != -INFINITY) {
+                            const float a_o = __expf(lse_val - mx), a_p = __expf(lse_p - mx);
+                            const float den = a_o + a_p;
+                            w_o = a_o / den * inv;
+                            w_p = a_p / den;
+                            lse_val = mx + __logf(den);
+                        }
+#pragma unroll
+                        for (int c = 0; c < D / 32; ++c) {
+                            uint32_t w[32], oc[32];
+#pragma unroll
+                            for (int i = 0; i < 32; ++i) w[i] = pr[c * 32 + i];
+                            quad_transpose(w, lane);
+                            tmem_ld32(tO + c * 32, oc);
+#pragma unroll
+                            for (int i = 0; i < 32; ++i)
+                                oc[i] = __float_as_uint(__uint_as_float(oc[i]) * w_o + __uint_as_float(w[i]) * w_p);
+                            tmem_st32(tO + c * 32, oc);
+                        }
+                        tmem_wait_st();
+                        inv = 1.f;
+                    }
+                    if (!alive) break;
+                }
+                // the whole row is read from tensor memory with one load and one wait
+                uint32_t o[D];
+                if (!empty) {
+                    if constexpr (D == 128) tmem_ld128(tO, o);
+                    else tmem_ld64(tO, o);
+                } else {
+#pragma unroll
+                    for (int i = 0; i < D; ++i) o[i] = 0u;
+                }
+                // where the row goes: the output, a Split-KV partial, or this CTA's cut partial
                 const long long grow = (static_cast<long long>(u_b) * p.H + u_h) * p.Sq + row;
-                const bool split_out = p.num_splits > 1;
                 float* o32 = nullptr;
-                if (split_out) {
+                int rows_left = p.Sq - row;
+                bool wide = p.wide_stores != 0;
+                if (part == kPartTail) {
+                    const long long slot = blockIdx.x;
+                    o32 = p.cut_part + (slot * (2 * kBlockM) + tile_row) * D;
+                    p.cut_part[static_cast<long long>(gridDim.x) * (2 * kBlockM) * D + slot * (2 * kBlockM) + tile_row] = lse_val;
+                    rows_left = kBlockM;                  // every row of the slot exists
+                    wide = true;                          // the workspace is 256-byte aligned
+                } else if (p.num_splits > 1) {
                     // dual mode stores one partial per CTA (split group), otherwise one per split
                     const long long prow =
                         ((static_cast<long long>(dual ? u_sgroup : split_t) * p.B + u_b) * p.H + u_h) *
@@ -965,18 +1100,8 @@ fa_mask_fwd_kernel(const __grid_constant__ CUtensorMap tm_q,
                     if (row_ok && p.lse != nullptr) p.lse[grow] = lse_val;
                 }
                 uint16_t* o16 = static_cast<uint16_t*>(p.out) + grow * D;
-                if (p.wide_stores) {
-                    // quad-transposed, line-sized stores (see quad_transpose); the whole row is
-                    // read from tensor memory with one load and one wait
-                    const int rows_left = p.Sq - row;
-                    uint32_t o[D];
-                    if (!empty) {
-                        if constexpr (D == 128) tmem_ld128(tO, o);
-                        else tmem_ld64(tO, o);
-                    } else {
-#pragma unroll
-                        for (int i = 0; i < D; ++i) o[i] = 0u;
-                    }
+                if (wide) {
+                    // quad-transposed, line-sized stores (see quad_transpose)
                     if (o32 != nullptr) {
 #pragma unroll
                         for (int c = 0; c < D / 32; ++c) {
@@ -1000,39 +1125,39 @@ fa_mask_fwd_kernel(const __grid_constant__ CUtensorMap tm_q,
                                        rows_left);
                         }
                     }
-                } else {
+                } else if (row_ok) {
+                    // an output that is only 16-byte aligned: each thread stores its own row
+                    if (o32 != nullptr) {
 #pragma unroll
-                    for (int c = 0; c < D / 32; ++c) {
-                        uint32_t o[32];
-                        if (!empty) {
-                            tmem_ld32(tO + c * 32, o);
-                        } else {
-#pragma unroll
-                            for (int i = 0; i < 32; ++i) o[i] = 0u;
+                        for (int i = 0; i < D; i += 4) {
+                            float4 f;
+                            f.x = __uint_as_float(o[i]) * inv;
+                            f.y = __uint_as_float(o[i + 1]) * inv;
+                            f.z = __uint_as_float(o[i + 2]) * inv;
+                            f.w = __uint_as_float(o[i + 3]) * inv;
+                            *reinterpret_cast<float4*>(o32 + i) = f;
                         }
-                        if (row_ok) {
-                            if (o32 != nullptr) {
+                    } else {
 #pragma unroll
-                                for (int i = 0; i < 32; i += 4) {
-                                    float4 f;
-                                    f.x = __uint_as_float(o[i]) * inv;
-                                    f.y = __uint_as_float(o[i + 1]) * inv;
-                                    f.z = __uint_as_float(o[i + 2]) * inv;
-                                    f.w = __uint_as_float(o[i + 3]) * inv;
-                                    *reinterpret_cast<float4*>(o32 + c * 32 + i) = f;
-                                }
-                            } else {
-#pragma unroll
-                                for (int i = 0; i < 32; i += 8) {
-                                    uint4 uu;
-                                    uu.x = pack2<BF16>(__uint_as_float(o[i]) * inv, __uint_as_float(o[i + 1]) * inv);
-                                    uu.y = pack2<BF16>(__uint_as_float(o[i + 2]) * inv, __uint_as_float(o[i + 3]) * inv);
-                                    uu.z = pack2<BF16>(__uint_as_float(o[i + 4]) * inv, __uint_as_float(o[i + 5]) * inv);
-                                    uu.w = pack2<BF16>(__uint_as_float(o[i + 6]) * inv, __uint_as_float(o[i + 7]) * inv);
-                                    *reinterpret_cast<uint4*>(o16 + c * 32 + i) = uu;
-                                }
-                            }
+                        for (int i = 0; i < D; i += 8) {
+                            uint4 uu;
+                            uu.x = pack2<BF16>(__uint_as_float(o[i]) * inv, __uint_as_float(o[i + 1]) * inv);
+                            uu.y = pack2<BF16>(__uint_as_float(o[i + 2]) * inv, __uint_as_float(o[i + 3]) * inv);
+                            uu.z = pack2<BF16>(__uint_as_float(o[i + 4]) * inv, __uint_as_float(o[i + 5]) * inv);
+                            uu.w = pack2<BF16>(__uint_as_float(o[i + 6]) * inv, __uint_as_float(o[i + 7]) * inv);
+                            *reinterpret_cast<uint4*>(o16 + i) = uu;
                         }
+                    }
+                }
+                if (part == kPartTail) {
+                    // publish: the partial rows of this warp, then its tag
+                    __threadfence();
+                    __syncwarp();
+                    if (lane == 0) {
+                        unsigned long long* tag = reinterpret_cast<unsigned long long*>(
+                            p.cut_part + static_cast<long long>(gridDim.x) * (2 * kBlockM) * (D + 1)) +
+                            static_cast<long long>(blockIdx.x) * 8 + warp;
+                        st_release_u64(tag, p.cut_tag);
                     }
                 }
                 // the next unit's first P.V overwrites O: every read above has completed
@@ -1333,6 +1458,26 @@ static bool mask_in_place(const FaMaskFwdArgs* a) {
            (a->mask_batch_stride % 8 == 0) && (sk8 <= a->mask_row_stride);
 }
 
+// Scratch of the unit cutting: per CTA 256 rows of fp32 O, 256 LSE values and 8 tags.
+static size_t cut_bytes(int ctas, int d) {
+    return align256(static_cast<size_t>(ctas) * (2 * kBlockM) * (d + 1) * sizeof(float) +
+                    static_cast<size_t>(ctas) * 8 * sizeof(unsigned long long));
+}
+
+// Tags of the unit cutting are unique per launch: a random start, then a counter.
+static std::atomic<unsigned long long> g_cut_tag{0};
+static unsigned long long next_cut_tag() {
+    unsigned long long cur = g_cut_tag.load();
+    if (cur == 0) {
+        unsigned long long seed = static_cast<unsigned long long>(
+            std::chrono::high_resolution_clock::now().time_since_epoch().count());
+        seed ^= reinterpret_cast<uintptr_t>(&g_cut_tag) * 0x9E3779B97F4A7C15ull;
+        seed = (seed * 0xBF58476D1CE4E5B9ull) | (1ull << 32);       // never 0
+        g_cut_tag.compare_exchange_strong(cur, seed);
+    }
+    return g_cut_tag.fetch_add(1) + 1;
+}
+
 static int make_plan(const FaMaskFwdArgs* a, FaMaskFwdPlan* plan) {
     int rc = validate(a);
     if (rc != FA_SM100_OK) return rc;
@@ -1404,9 +1549,19 @@ static int make_plan(const FaMaskFwdArgs* a, FaMaskFwdPlan* plan) {
     }
     // Tile skipping: single pass over the keys, at least two key blocks, list fits the CTA.
     plan->tile_skip = (splits == 1 && nb >= 4 && nb <= kMaxListBlocks && a->seqlen_q > 0 &&
-                       a->no_tile_skip == 0) ? 1 : 0;
+                       (a->disable & FA_SM100_NO_TILE_SKIP) == 0) ? 1 : 0;
     // (block flags, then the counter the attention kernel hands out its units from)
     if (plan->tile_skip) ws += align256(static_cast<size_t>(a->batch) * m_pairs * nb) + 256;
+    // More single-pass units than CTAs: the CTAs take equal shares of all (unit, key block)
+    // steps and a unit cut at a share boundary is merged through a per-CTA slot of scratch.
+    plan->unit_cut = 0;
+    if (!dual && splits == 1 && units > dev->sm_count && units % dev->sm_count != 0 &&
+        (a->disable & FA_SM100_NO_UNIT_CUT) == 0) {
+        long long pieces = dev->sm_count / (units % dev->sm_count);
+        if (pieces > nb) pieces = nb;
+        if (pieces >= 2) plan->unit_cut = static_cast<int32_t>(pieces);
+    }
+    if (plan->unit_cut) ws += cut_bytes(plan->grid_x, d);
     plan->workspace_bytes = ws;
     return FA_SM100_OK;
 }
@@ -1784,6 +1939,12 @@ static int forward(const FaMaskFwdArgs* a, void* workspace, size_t workspace_byt
     kp.dual = plan.dual_split;
     kp.split_groups = plan.dual_split ? ceil_div(plan.num_splits, 2) : plan.num_splits;
     kp.total_units = kp.m_pairs * kp.split_groups * a->heads * a->batch;
+    if (plan.unit_cut) {
+        kp.cut_units = plan.unit_cut;
+        kp.cut_part = reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) + plan.workspace_bytes -
+                                               cut_bytes(plan.grid_x, d));
+        kp.cut_tag = next_cut_tag();
+    }
     kp.out_fp32 = a->out_fp32;
     kp.wide_stores = (((reinterpret_cast<uintptr_t>(a->out) | reinterpret_cast<uintptr_t>(o_part)) & 31u) == 0) ? 1 : 0;
     kp.scale = static_cast<float>(1.0 / std::sqrt(static_cast<double>(d)));

@@ -230,6 +230,31 @@ __device__ __forceinline__ void stg256(void* gptr, const uint32_t* r) {
                  : "memory");
 }
 
+// Loads that bypass the L1 (data another CTA of the same launch wrote), and the acquire /
+// release pair that orders them.
+__device__ __forceinline__ uint4 ld_cg_v4(const void* gptr) {
+    uint4 v;
+    asm volatile("ld.global.cg.v4.u32 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(gptr) : "memory");
+    return v;
+}
+
+__device__ __forceinline__ float ld_cg_f32(const float* gptr) {
+    float v;
+    asm volatile("ld.global.cg.f32 %0, [%1];" : "=f"(v) : "l"(gptr) : "memory");
+    return v;
+}
+
+__device__ __forceinline__ unsigned long long ld_acquire_u64(const unsigned long long* gptr) {
+    unsigned long long v;
+    asm volatile("ld.acquire.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(gptr) : "memory");
+    return v;
+}
+
+__device__ __forceinline__ void st_release_u64(unsigned long long* gptr, unsigned long long v) {
+    asm volatile("st.release.gpu.global.u64 [%0], %1;" ::"l"(gptr), "l"(v) : "memory");
+}
+
 __device__ __forceinline__ uint32_t lds16(uint32_t saddr) {
     uint16_t v;
     asm volatile("ld.shared.u16 %0, [%1];" : "=h"(v) : "r"(saddr) : "memory");

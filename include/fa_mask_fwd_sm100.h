@@ -42,6 +42,13 @@ enum {
 
 enum { FA_SM100_FP16 = 0, FA_SM100_BF16 = 1 };
 
+/* Bits of FaMaskFwdArgs.disable.  Neither changes what is computed, only how. */
+enum {
+    FA_SM100_NO_TILE_SKIP = 1,  /* visit every key block even where the mask hides it entirely */
+    FA_SM100_NO_UNIT_CUT = 2    /* every (query pair, head, batch) unit is finished by one CTA, so the
+                                 * result does not depend on the number of SMs */
+};
+
 #define FA_SM100_MAX_SPLITS 128
 
 /*
@@ -84,7 +91,7 @@ typedef struct FaMaskFwdArgs {
     int32_t dtype;              /* FA_SM100_FP16 / FA_SM100_BF16 */
     int32_t num_splits;         /* 0 = choose, 1 = never split, n = force n KV splits */
     int32_t out_fp32;           /* 1: `out` is fp32 (normalised partial for a cross-GPU merge) */
-    int32_t no_tile_skip;       /* 1: visit every key block even where the mask hides it entirely */
+    int32_t disable;            /* bit set of FA_SM100_NO_*: optimisations the caller switches off */
 } FaMaskFwdArgs;
 
 /* What the launcher decided for a set of arguments; for tests and tuning. */
@@ -104,7 +111,10 @@ typedef struct FaMaskFwdPlan {
                                  * kernel does not visit them (exact: their weights are 0).  The
                                  * launcher drops the pre-pass for a while after it found nothing to
                                  * skip twice in a row for the same mask buffer and shape. */
-    int32_t reserved;
+    int32_t unit_cut;           /* P >= 2: there are more single-pass units than CTAs and the R units
+                                 * of the last, partial round are done by P = SMs / R CTAs each (one
+                                 * piece of the key blocks per CTA, merged through the workspace)
+                                 * instead of leaving most SMs idle; 0: every unit is done by one CTA */
     uint64_t workspace_bytes;
 } FaMaskFwdPlan;
 

@@ -317,6 +317,29 @@ def test_splitkv_single_tile_dual_mode(dtype, case):
     assert np.abs(lse.cpu().numpy() - ref_lse).max() < 2e-3
 
 
+# ---------------------------------------------------------------- units of the last round cut in pieces
+@pytest.mark.parametrize("case", [(2, 16, 16, 1280, 640, 128, torch.bfloat16),
+                                  (3, 12, 4, 1250, 900, 64, torch.float16),
+                                  (1, 40, 8, 1024, 300, 128, torch.float16)])
+def test_units_of_the_last_round_are_cut(case):
+    """More single-pass units than SMs: the units of the last, partial round are done in pieces
+    by several CTAs each and merged.  The result must match the oracle and, within rounding,
+    the run that keeps every unit whole."""
+    b, h, hk, sq, sk, d, dtype = case
+    q, k, v, m = make_case(b, h, hk, sq, sk, d, dtype, "drop_bias", seed=23)
+    q, k, v, m = _cuda(q, k, v, m)
+    out_cut, lse_cut, plan = run_cabi(q, k, v, m, want_lse=True, no_tile_skip=1)
+    out_whole, lse_whole, plan_whole = run_cabi(q, k, v, m, want_lse=True, no_tile_skip=1, no_unit_cut=1)
+    assert plan.unit_cut >= 2 and plan_whole.unit_cut == 0 and plan.num_splits == 1
+    assert plan.grid_x == plan.sm_count
+    check_against_oracle(out_cut, q, k, v, m, f"cut{case}")
+    assert (out_cut.float() - out_whole.float()).abs().max().item() <= 4e-3
+    assert torch.allclose(lse_cut, lse_whole, atol=1e-4, rtol=1e-5)
+    # twice in a row on the same scratch: the tags of the first launch must not satisfy the second
+    out_again, _, _ = run_cabi(q, k, v, m, want_lse=True, no_tile_skip=1)
+    assert torch.equal(out_again, out_cut)
+
+
 # ---------------------------------------------------------------- tile skipping
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("case", [(2, 4, 2, 768, 768, 128, 160), (1, 2, 2, 1000, 1411, 64, 300),

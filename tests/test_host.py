@@ -50,9 +50,16 @@ def test_plan_of_the_five_configurations():
     p = _plan(batch=4, heads=16, heads_k=16, seqlen_q=2048, seqlen_k=2048)
     # 8 * 16 * 4 = 512 units; pair mode is persistent: one CTA per SM takes every grid_x-th unit
     assert (p.num_splits, p.kv_blocks, p.grid_x, p.q_tiles_per_cta) == (1, 16, min(512, sm), 2)
-    # block flags (4 * 8 * 16 bytes -> 512) + the unit counter
-    assert p.tile_skip == 1 and p.workspace_bytes == 512 + 256 and p.mask_repitched == 0 and p.threads == 384
-    assert _plan(batch=4, heads=16, heads_k=16, seqlen_q=2048, seqlen_k=2048, no_tile_skip=1).workspace_bytes == 0
+    # block flags (4 * 8 * 16 bytes -> 512) + the unit counter; more units than CTAs: the units of
+    # the last, partial round are cut in pieces, which takes per CTA 256 rows of fp32 O + LSE and 8 tags
+    pieces = min(sm // (512 % sm), 16) if 512 > sm and 512 % sm else 0     # CTAs per unit of the last round
+    pieces = pieces if pieces >= 2 else 0
+    cut = -(-(p.grid_x * 256 * (128 + 1) * 4 + p.grid_x * 8 * 8) // 256) * 256 if pieces else 0
+    assert p.unit_cut == pieces
+    assert p.tile_skip == 1 and p.workspace_bytes == 512 + 256 + cut and p.mask_repitched == 0 and p.threads == 384
+    assert _plan(batch=4, heads=16, heads_k=16, seqlen_q=2048, seqlen_k=2048, no_tile_skip=1).workspace_bytes == cut
+    assert _plan(batch=4, heads=16, heads_k=16, seqlen_q=2048, seqlen_k=2048, no_tile_skip=1,
+                 no_unit_cut=1).workspace_bytes == 0
     p = _plan(batch=1, heads=16, heads_k=16, seqlen_q=128, seqlen_k=32768)
     assert p.kv_blocks == 256 and p.num_splits == 2 * max(1, sm // 16) and p.q_tiles_per_cta == 1
     assert p.dual_split == 1 and p.grid_x == 16 * ((p.num_splits + 1) // 2)
