@@ -49,8 +49,8 @@ FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustain
 # dram__bytes_read.sum + dram__bytes_write.sum of one attention-kernel launch, from
 # the ncu captures summarised under profiles/ (None until a capture exists).
 NCU_TRAFFIC_BYTES = {
-    "standard": 154.9e6,        # 135.2 MB read + 19.7 MB written (ncu summary of the standard workload)
-    "splitkv_long": 285.2e6,    # 277.95 MB read + 7.27 MB written (ncu summary of the long-context workload)
+    "standard": 153.3e6,        # 134.9 MB read + 18.4 MB written (ncu summary of the standard workload)
+    "splitkv_long": 281.6e6,    # 277.46 MB read + 4.11 MB written (ncu summary of the long-context workload)
 }
 
 
@@ -312,6 +312,8 @@ def run_ours(args, w):
             time.sleep(0.05)
 
     for _ in range(max(3, args.warmup)):
+        if not rotate:
+            flush.zero_()                   # the warm-up steps are the timed steps, untimed
         step_kernel()
     torch.cuda.synchronize(dev)
 

@@ -1754,15 +1754,18 @@ static int status_pointer(DeviceInfo* dev) {
 // kernel counts the skippable regions into a word of mapped pinned host memory, which the
 // host reads on a LATER call without synchronising anything.  Two pre-passes in a row that
 // found nothing switch it off for the next kSkipHoldoff calls with that mask; then it is
-// tried again.  Only whether the optimisation runs depends on this; results never do.
+// tried again, and every further miss doubles the pause up to kSkipHoldoffMax calls.  Only
+// whether the optimisation runs depends on this; results never do.
 constexpr int kHintSlots = 16;
 constexpr int kSkipHoldoff = 30;
+constexpr int kSkipHoldoffMax = 960;
 struct SkipHint {
     const void* mask = nullptr;
     long long bs = 0, rs = 0;
     int B = 0, Sq = 0, Sk = 0, dtype = 0, device = 0;
     int zero_streak = 0;
     int holdoff = 0;
+    int pause = kSkipHoldoff;     // length of the next pause
     bool ran_last = false;
     bool valid = false;
 };
@@ -1819,12 +1822,14 @@ static bool want_classify(const FaMaskFwdArgs* a, const void* mask, long long bs
         if (*word == 1) {
             if (++h.zero_streak >= 2) {
                 h.zero_streak = 0;
-                h.holdoff = kSkipHoldoff;
+                h.holdoff = h.pause;
+                h.pause = h.pause * 2 > kSkipHoldoffMax ? kSkipHoldoffMax : h.pause * 2;
                 h.ran_last = false;
                 return false;
             }
         } else if (*word > 1) {
             h.zero_streak = 0;
+            h.pause = kSkipHoldoff;
         }
     }
     *word = 0;
