@@ -6,9 +6,11 @@
 mirrors ``from custom_ops import ops`` of the reference (``__init__.py:1222``,
 ``recsys.py:641-656``).  Importing the package compiles and loads nothing; the
 native libraries are built (in-tree) and loaded on first use.
+``mha_fwd_with_mask_from_host`` is the same operator for operands in host memory.
 """
+from .host_io import mha_fwd_with_mask_from_host  # noqa: F401
 from .recsys import CustomOps, CustomOpsError, FAOps, RecsysOps  # noqa: F401
 
 ops = RecsysOps()
 
-__all__ = ["ops", "RecsysOps", "FAOps", "CustomOps", "CustomOpsError"]
+__all__ = ["ops", "RecsysOps", "FAOps", "CustomOps", "CustomOpsError", "mha_fwd_with_mask_from_host"]

@@ -382,3 +382,24 @@ def test_tile_skipping_everything_masked_and_trap_columns():
     out, _, plan = run_cabi(q, k, v, m, num_splits=1)
     assert plan.tile_skip == 1
     check_against_oracle(out, q, k, v, m[:, :, :, :700].contiguous(), "trap columns")
+
+
+# ---------------------------------------------------------------- operands in host memory
+@pytest.mark.parametrize("chunk", [1, 2, 5])
+def test_host_memory_entry_point_matches_the_operator(chunk):
+    """``mha_fwd_with_mask_from_host`` pipelines batch elements over three streams; its result
+    is bit-identical to the operator on device tensors, for any chunking."""
+    from custom_ops_b200 import mha_fwd_with_mask_from_host, ops
+    q, k, v, m = make_case(3, 4, 2, 200, 333, 64, torch.bfloat16, "drop_bias", seed=29)
+    ref = ops.mha_fwd_with_mask(*_cuda(q, k, v, m)).cpu()
+    qp, kp, vp, mp = (t.pin_memory() for t in (q, k, v, m))
+    out = mha_fwd_with_mask_from_host(qp, kp, vp, mp, batch_chunk=chunk)
+    torch.cuda.current_stream().synchronize()
+    assert out.is_pinned() and torch.equal(out, ref)
+    out2 = torch.empty_like(out).pin_memory()
+    assert mha_fwd_with_mask_from_host(qp, kp, vp, mp, out2, batch_chunk=chunk) is out2
+    torch.cuda.synchronize()
+    assert torch.equal(out2, ref)
+    with pytest.raises(ValueError):
+        mha_fwd_with_mask_from_host(qp.cuda(), kp, vp, mp)
+
