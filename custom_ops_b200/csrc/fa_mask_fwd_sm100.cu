@@ -1945,10 +1945,14 @@ static int forward(const FaMaskFwdArgs* a, void* workspace, size_t workspace_byt
     kp.split_groups = plan.dual_split ? ceil_div(plan.num_splits, 2) : plan.num_splits;
     kp.total_units = kp.m_pairs * kp.split_groups * a->heads * a->batch;
     if (plan.unit_cut) {
-        kp.cut_units = plan.unit_cut;
-        kp.cut_part = reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) + plan.workspace_bytes -
-                                               cut_bytes(plan.grid_x, d));
-        kp.cut_tag = next_cut_tag();
+        uint8_t* slots = static_cast<uint8_t*>(workspace) + plan.workspace_bytes - cut_bytes(plan.grid_x, d);
+        // the partials are written with 256-bit stores; a workspace that is only 16-byte
+        // aligned keeps every unit whole instead (same grid, every grid-th unit per CTA)
+        if ((reinterpret_cast<uintptr_t>(slots) & 31u) == 0) {
+            kp.cut_units = plan.unit_cut;
+            kp.cut_part = reinterpret_cast<float*>(slots);
+            kp.cut_tag = next_cut_tag();
+        }
     }
     kp.out_fp32 = a->out_fp32;
     kp.wide_stores = (((reinterpret_cast<uintptr_t>(a->out) | reinterpret_cast<uintptr_t>(o_part)) & 31u) == 0) ? 1 : 0;
