@@ -44,16 +44,20 @@ def mha_fwd_with_mask_from_host(q: torch.Tensor, k: torch.Tensor, v: torch.Tenso
 
     if q.is_cuda or k.is_cuda or v.is_cuda or mask.is_cuda:
         raise ValueError("mha_fwd_with_mask_from_host takes host tensors; use ops.mha_fwd_with_mask")
-    device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
-    if device.index is None:
-        device = torch.device("cuda", torch.cuda.current_device())
+    if q.dim() != 4 or k.dim() != 4 or v.dim() != 4 or mask.dim() != 4:
+        raise ValueError("q, k, v and mask must be 4-D")
     B = q.shape[0]
     if k.shape[0] != B or v.shape[0] != B or mask.shape[0] != B:
         raise ValueError("q, k, v and mask must have the same batch size")
+    if out is not None and (out.is_cuda or out.shape != q.shape or out.dtype != q.dtype):
+        raise ValueError("out must be a host tensor of q's shape and dtype")
+    if not torch.cuda.is_available():
+        raise RuntimeError("mha_fwd_with_mask_from_host needs a CUDA device: there is no CPU path")
+    device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    if device.index is None:
+        device = torch.device("cuda", torch.cuda.current_device())
     if out is None:
         out = torch.empty(q.shape, dtype=q.dtype, pin_memory=True)
-    elif out.is_cuda or out.shape != q.shape or out.dtype != q.dtype:
-        raise ValueError("out must be a host tensor of q's shape and dtype")
     batch_chunk = max(1, int(batch_chunk))
 
     s_in, s_run, s_out = _Streams.get(device)

@@ -320,7 +320,11 @@ def test_splitkv_single_tile_dual_mode(dtype, case):
 # ---------------------------------------------------------------- units of the last round cut in pieces
 @pytest.mark.parametrize("case", [(2, 16, 16, 1280, 640, 128, torch.bfloat16),
                                   (3, 12, 4, 1250, 900, 64, torch.float16),
-                                  (1, 40, 8, 1024, 300, 128, torch.float16)])
+                                  (1, 40, 8, 1024, 300, 128, torch.float16),
+                                  # one unit left over: cut into as many pieces as it has key blocks
+                                  (1, 149, 149, 200, 1000, 64, torch.bfloat16),
+                                  # two pieces per unit, the first one key block longer
+                                  (1, 111, 37, 512, 1100, 128, torch.bfloat16)])
 def test_units_of_the_last_round_are_cut(case):
     """More single-pass units than SMs: the units of the last, partial round are done in pieces
     by several CTAs each and merged.  The result must match the oracle and, within rounding,

@@ -213,3 +213,22 @@ def test_mask_recipes():
     q, k, v, mm = make_inputs(workloads.small_analogue(WORKLOADS["ragged_items"], 20, 83, H=8))
     assert q.shape == (1, 8, 20, 128) and k.shape == (1, 2, 83, 128) and mm.shape == (1, 1, 20, 83)
     assert abs(q.float().std().item() - 0.5) < 0.05
+
+
+def test_host_memory_entry_point_checks_its_arguments():
+    """Argument errors of ``mha_fwd_with_mask_from_host`` are raised before any CUDA call, and
+    without a device the call fails loudly instead of computing on the CPU."""
+    from custom_ops_b200 import mha_fwd_with_mask_from_host
+    q = torch.zeros(2, 2, 8, 64, dtype=torch.bfloat16)
+    k = torch.zeros(2, 2, 8, 64, dtype=torch.bfloat16)
+    m = torch.zeros(2, 1, 8, 8, dtype=torch.bfloat16)
+    with pytest.raises(ValueError):
+        mha_fwd_with_mask_from_host(q, k[:1], k, m)
+    with pytest.raises(ValueError):
+        mha_fwd_with_mask_from_host(q, k, k, m[0])
+    with pytest.raises(ValueError):
+        mha_fwd_with_mask_from_host(q, k, k, m, torch.zeros(2, 2, 8, 64))
+    if not torch.cuda.is_available():
+        with pytest.raises(RuntimeError):
+            mha_fwd_with_mask_from_host(q, k, k, m)
+
