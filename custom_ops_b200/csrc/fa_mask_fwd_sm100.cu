@@ -866,11 +866,15 @@ fa_mask_fwd_kernel(const __grid_constant__ CUtensorMap tm_q,
                 const float m_new = fmaxf(m_ref, mt);
                 const bool need = (m_new - m_ref) > kRescaleThreshold;  // NaN (-inf - -inf) -> false
                 float alpha = 1.f;
+                // A row that sees its first visible key only now has nothing worth rescaling in O
+                // (at most the 1e-38 dust of the polynomial exponential times V, which vanishes
+                // against the first real term), so it does not ask for the pass over O below.
+                const bool rescale_o = need && (m_ref != -INFINITY);
                 if (need) {
                     alpha = ex2((m_ref - m_new) * kLog2e);                // m_ref = -inf -> 0
                     m_ref = m_new;
                 }
-                if (j > 0 && __any_sync(0xffffffffu, need)) {
+                if (j > 0 && __any_sync(0xffffffffu, rescale_o)) {
                     // PV of the previous block finished before this block's S was committed.
 #pragma unroll
                     for (int c = 0; c < D / 32; ++c) {
