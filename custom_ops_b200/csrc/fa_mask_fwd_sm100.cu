@@ -55,6 +55,7 @@
 #include <chrono>
 #include <cstring>
 #include <mutex>
+#include <type_traits>
 
 #include "../../include/fa_mask_fwd_sm100.h"
 #include "arch_targets.h"
@@ -1307,15 +1308,27 @@ fa_mask_classify_kernel(const uint16_t* __restrict__ mask, long long bs, long lo
     const int col = nt * kBlockN + vec * 8;
     const uint16_t neg_inf = static_cast<uint16_t>(neg_inf2 & 0xffffu);
     int visible = 0;
-    for (int pass = 0; pass < 2 * kBlockM / 16; ++pass) {
-        const int row = mp * 2 * kBlockM + pass * 16 + rsub;
-        if (row < Sq && col < Sk) {
-            const uint16_t* src = mask + b * bs + row * rs + col;
-            const uint4 v = __ldg(reinterpret_cast<const uint4*>(src));
+    // 16 passes of 16 rows in two rounds: 4 passes, a block-wide vote (a region with anything
+    // visible usually ends here), then the other 12 with all their loads in flight at once.
+    // (One pass per vote made a fully masked region cost 16 round trips to memory.)
+    auto scan = [&](auto passes_tag, int pass0) {
+        constexpr int kPasses = decltype(passes_tag)::value;
+        uint4 v[kPasses];
+        bool in[kPasses];
+#pragma unroll
+        for (int u = 0; u < kPasses; ++u) {
+            const int row = mp * 2 * kBlockM + (pass0 + u) * 16 + rsub;
+            in[u] = row < Sq && col < Sk;
+            v[u] = make_uint4(neg_inf2, neg_inf2, neg_inf2, neg_inf2);
+            if (in[u]) v[u] = __ldg(reinterpret_cast<const uint4*>(mask + b * bs + row * rs + col));
+        }
+#pragma unroll
+        for (int u = 0; u < kPasses; ++u) {
+            if (!in[u]) continue;
             if (col + 8 <= Sk) {
-                visible |= (v.x != neg_inf2) | (v.y != neg_inf2) | (v.z != neg_inf2) | (v.w != neg_inf2);
+                visible |= (v[u].x != neg_inf2) | (v[u].y != neg_inf2) | (v[u].z != neg_inf2) | (v[u].w != neg_inf2);
             } else {
-                const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+                const uint32_t w[4] = {v[u].x, v[u].y, v[u].z, v[u].w};
 #pragma unroll
                 for (int e = 0; e < 8; ++e) {
                     const uint16_t x = static_cast<uint16_t>(w[e >> 1] >> ((e & 1) * 16));
@@ -1323,10 +1336,12 @@ fa_mask_classify_kernel(const uint16_t* __restrict__ mask, long long bs, long lo
                 }
             }
         }
-        if (__syncthreads_or(visible)) {
-            visible = 1;
-            break;
-        }
+    };
+    scan(std::integral_constant<int, 4>{}, 0);
+    visible = __syncthreads_or(visible) ? 1 : 0;
+    if (!visible) {
+        scan(std::integral_constant<int, 12>{}, 4);
+        visible = __syncthreads_or(visible) ? 1 : 0;
     }
     if (threadIdx.x == 0) {
         flags[(static_cast<long long>(b) * gridDim.y + mp) * gridDim.x + nt] = visible ? 1 : 0;
