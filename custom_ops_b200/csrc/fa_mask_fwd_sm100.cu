@@ -1377,7 +1377,53 @@ fa_mask_repitch_kernel(const uint16_t* __restrict__ src, uint16_t* __restrict__ 
     const int row = static_cast<int>(r % Sq);
     const uint16_t* s = src + b * src_bs + row * src_rs;
     uint16_t* d = dst + r * pitch;
-    for (int c = threadIdx.x; c < pitch; c += blockDim.x) d[c] = (c < Sk) ? s[c] : uint16_t(0);
+    // One 16-byte vector of the destination per thread and step.  The source row starts on
+    // any 2-byte boundary: its bytes are fetched as the two aligned 16-byte vectors around
+    // them and shifted into place (the misalignment is the same for the whole row).
+    const uintptr_t s_addr = reinterpret_cast<uintptr_t>(s);
+    const unsigned mis = static_cast<unsigned>(s_addr & 15u);         // even, 0..14
+    const uint4* s16 = reinterpret_cast<const uint4*>(s_addr - mis);
+    const unsigned word_off = mis >> 2, bit_shift = (mis & 3u) * 8u;
+    for (int c = threadIdx.x * 8; c < pitch; c += blockDim.x * 8) {
+        uint4 out = make_uint4(0u, 0u, 0u, 0u);
+        if (c < Sk) {
+            const int valid = min(8, Sk - c);                         // elements wanted from the source
+            const uint4 lo = __ldg(s16 + (c >> 3));
+            // the second vector only when a wanted byte lies in it (never reads past the vector
+            // that holds the row's last element)
+            uint4 hi = make_uint4(0u, 0u, 0u, 0u);
+            if (mis + 2u * valid > 16u) hi = __ldg(s16 + (c >> 3) + 1);
+            const uint32_t w[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
+            uint32_t o[4];
+            switch (word_off) {                                       // uniform over the CTA
+                case 0:
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) o[k] = __funnelshift_r(w[k], w[k + 1], bit_shift);
+                    break;
+                case 1:
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) o[k] = __funnelshift_r(w[k + 1], w[k + 2], bit_shift);
+                    break;
+                case 2:
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) o[k] = __funnelshift_r(w[k + 2], w[k + 3], bit_shift);
+                    break;
+                default:
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) o[k] = __funnelshift_r(w[k + 3], k + 4 < 8 ? w[k + 4] : 0u, bit_shift);
+                    break;
+            }
+            if (valid < 8) {                                          // pad columns are 0
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    if (2 * k >= valid) o[k] = 0u;
+                    else if (2 * k + 1 >= valid) o[k] &= 0xffffu;
+                }
+            }
+            out = make_uint4(o[0], o[1], o[2], o[3]);
+        }
+        *reinterpret_cast<uint4*>(d + c) = out;
+    }
 }
 
 // ---------------------------------------------------------------------------------
