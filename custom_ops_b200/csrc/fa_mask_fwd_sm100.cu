@@ -1069,6 +1069,11 @@ fa_mask_fwd_kernel(const __grid_constant__ CUtensorMap tm_q,
                             tmem_st32(tO + c * 32, oc);
                         }
                         tmem_wait_st();
+                        // The tag is taken back once the partial has been read (every load above
+                        // has delivered its data), so a launch that repeats this one's tag - a
+                        // replayed CUDA graph - cannot mistake this partial for its own.
+                        __syncwarp();
+                        if (lane == 0) st_release_u64(const_cast<unsigned long long*>(tags) + slot * 8 + warp, 0ull);
                         inv = 1.f;
                     }
                     if (!alive) break;

@@ -344,6 +344,37 @@ def test_units_of_the_last_round_are_cut(case):
     assert torch.equal(out_again, out_cut)
 
 
+def test_unit_cut_survives_cuda_graph_replay():
+    """A captured launch repeats its tag on every replay; the head pieces take the tags back
+    after reading, so a replay on new data must not pick up the previous replay's partials."""
+    b, h, hk, sq, sk, d = 2, 16, 16, 1280, 640, 128
+    q, k, v, m = _cuda(*make_case(b, h, hk, sq, sk, d, torch.bfloat16, "drop_bias", seed=31))
+    out = torch.empty_like(q)
+    args = _cabi.make_args(q=q.data_ptr(), k=k.data_ptr(), v=v.data_ptr(), mask=m.data_ptr(), out=out.data_ptr(),
+                           batch=b, heads=h, heads_k=hk, seqlen_q=sq, seqlen_k=sk, head_dim=d, dtype=_cabi.BF16,
+                           no_tile_skip=1)
+    assert _cabi.plan(args).unit_cut >= 2
+    nbytes = _cabi.workspace_bytes(args)
+    ws = torch.empty(nbytes, dtype=torch.uint8, device="cuda")
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        _cabi.forward(args, ws.data_ptr(), nbytes, side.cuda_stream)      # set-up outside the capture
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        _cabi.forward(args, ws.data_ptr(), nbytes, torch.cuda.current_stream().cuda_stream)
+    for seed in (32, 33):
+        q2, k2, v2, _ = _cuda(*make_case(b, h, hk, sq, sk, d, torch.bfloat16, "drop_bias", seed=seed))
+        q.copy_(q2); k.copy_(k2); v.copy_(v2)
+        graph.replay()
+        torch.cuda.synchronize()
+        eager, _, _ = run_cabi(q, k, v, m, no_tile_skip=1)
+        assert torch.equal(out, eager)
+    assert _cabi.device_status(0, clear=True) == 0
+
+
 # ---------------------------------------------------------------- tile skipping
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("case", [(2, 4, 2, 768, 768, 128, 160), (1, 2, 2, 1000, 1411, 64, 300),
