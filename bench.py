@@ -51,8 +51,8 @@ FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustain
 LEAD_IN_STEPS = 2      # untimed steps between the barrier and the first timed step (clock ramp)
 
 NCU_TRAFFIC_BYTES = {
-    "standard": 153.3e6,        # 134.9 MB read + 18.4 MB written (ncu summary of the standard workload)
-    "splitkv_long": 281.6e6,    # 277.46 MB read + 4.11 MB written (ncu summary of the long-context workload)
+    "standard": 154.5e6,        # 135.0 MB read + 19.5 MB written (ncu summary of the standard workload)
+    "splitkv_long": 282.1e6,    # 277.45 MB read + 4.61 MB written (ncu summary of the long-context workload)
 }
 
 
