@@ -24,10 +24,8 @@ from typing import Optional
 import torch
 
 from . import build as _build
-
-
-class CustomOpsError(RuntimeError):
-    """Loader / deployment contract violation (reference ``__init__.py:71``)."""
+from . import deploy as _deploy
+from .deploy import CustomOpsError
 
 
 _LIBRARY_LOCK = threading.RLock()
@@ -75,6 +73,7 @@ class CustomOps:
     namespace: str = ""
     so_name: str = ""
     requires_cuda: bool = True
+    build_version: str = "1"       # bump when a rebuild must not be mistaken for an older export
     required_ops: list = []
     optional_ops: list = []
     op_schemas: dict = {}
@@ -86,6 +85,7 @@ class CustomOps:
         self._load_error: Optional[str] = None
         self._fake_ops_registered: set = set()
         self._library_path: Optional[str] = None
+        self._metadata_path: Optional[str] = None
 
     # -- configuration -------------------------------------------------------
     @property
@@ -119,6 +119,28 @@ class CustomOps:
 
     def prebuilt_path(self) -> str:
         raise NotImplementedError
+
+    def companion_libraries(self) -> list:
+        """Other shared libraries the operator library needs beside it (``$ORIGIN`` rpath)."""
+        return []
+
+    def source_fingerprint(self) -> str:
+        """sha256 over the contents of every source and header of the group."""
+        files = list(self.get_sources())
+        for d in self.get_include_dirs():
+            for root, _, names in sorted(os.walk(d)):
+                files += [os.path.join(root, n) for n in sorted(names)
+                          if n.endswith((".h", ".hpp", ".cuh", ".cu", ".cpp"))]
+        return _deploy.json_hash({os.path.basename(p): _deploy.file_sha256(p) for p in sorted(set(files))})
+
+    def export(self, directory: str, *, force: bool = False, verbose: bool = False) -> str:
+        """Offline build for deployment: libraries + JSON sidecar into ``directory``; nothing is
+        loaded (reference ``__init__.py:654-729``).  Returns the exported library's path."""
+        return _deploy.export_group(self, directory, force=force, verbose=verbose)
+
+    @property
+    def metadata_path(self) -> Optional[str]:
+        return self._metadata_path
 
     def register_fake_impls(self) -> None:
         pass
@@ -155,13 +177,21 @@ class CustomOps:
         with _LIBRARY_LOCK:
             real = os.path.realpath(path)
             if real in _LOADED_LIBRARIES:
+                if _LOADED_LIBRARIES[real] is None:
+                    raise CustomOpsError(f"{path} failed to load before; it is not tried again")
                 return
             for name in self.required_ops:
                 if _has_schema(f"{self.namespace}::{name}"):
+                    # also a byte-identical copy under another name: the dispatcher keeps one
+                    # registration per operator, a second dlopen would abort the process
                     raise CustomOpsError(
                         f"{self.namespace}::{name} is already registered by another library; "
                         f"two providers of one operator cannot share a process")
-            torch.ops.load_library(path)
+            try:
+                torch.ops.load_library(path)
+            except Exception:
+                _LOADED_LIBRARIES[real] = None          # never retried, never replaced
+                raise
             _LOADED_LIBRARIES[real] = type(self).__name__
 
     def load(self) -> "CustomOps":
@@ -195,16 +225,41 @@ class CustomOps:
                 warnings.warn(f"[{type(self).__name__}] load failed: {self._load_error}")
         return self
 
-    def load_precompiled(self, path: Optional[str] = None) -> "CustomOps":
-        """Strict load of an already built library; raises on any problem."""
+    def load_precompiled(self, path: Optional[str] = None,
+                         metadata_path: Optional[str] = None) -> "CustomOps":
+        """Strict load of an exported library (see :meth:`export`); raises on any problem and
+        never compiles.  Everything the JSON sidecar allows to be checked is checked before the
+        library is dlopen'ed (reference ``__init__.py:936-979``).  Without ``path`` the in-tree
+        build is loaded, which has no sidecar and is only checked after loading."""
         with _LIBRARY_LOCK:
-            path = path or self.prebuilt_path()
-            if not os.path.exists(path):
-                raise CustomOpsError(f"precompiled library not found: {path}")
-            self._dlopen_library(path)
-            self._verify_ops()
-            self.register_fake_impls()
+            if self._loaded:
+                same = path is None or os.path.realpath(path) == os.path.realpath(self._library_path or "")
+                if not same:
+                    raise CustomOpsError(
+                        f"{type(self).__name__} already loaded {self._library_path}; a process keeps one "
+                        f"provider per operator")
+                return self
+            metadata = None
+            if path is None:
+                path = self.prebuilt_path()
+                if not os.path.exists(path):
+                    raise CustomOpsError(f"precompiled library not found: {path}")
+            else:
+                metadata = _deploy.check_precompiled(self, path, metadata_path)
+            try:
+                self._dlopen_library(path)
+                self._verify_ops()
+                self.register_fake_impls()
+                has_meta = torch._C._dispatch_has_kernel_for_dispatch_key
+                for name in self.fake_ops:
+                    if not has_meta(f"{self.namespace}::{name}", "Meta"):
+                        raise CustomOpsError(f"{self.namespace}::{name} has no Meta kernel")
+            except Exception as e:
+                self._loaded = False
+                self._load_error = f"{type(e).__name__}: {e}"
+                raise
             self._library_path = path
+            self._metadata_path = (metadata_path or _deploy.sidecar_path(path)) if metadata else None
             self._loaded = True
             self._load_error = None
         return self
@@ -263,6 +318,9 @@ class FAOps(CustomOps):
     def prebuilt_path(self) -> str:
         return _build.TORCH_SO
 
+    def companion_libraries(self) -> list:
+        return [_build.CABI_SO]
+
     def register_fake_impls(self) -> None:
         self.register_fake_for("mha_fwd_with_mask", lambda q, k, v, mask: torch.empty_like(q))
 
@@ -310,11 +368,12 @@ class RecsysOps:
                 inst.load()
             return inst
 
-    def load_precompiled(self, group: str = "fa", path: Optional[str] = None) -> "RecsysOps":
+    def load_precompiled(self, group: str = "fa", path: Optional[str] = None,
+                         metadata_path: Optional[str] = None) -> "RecsysOps":
         with self._lock:
             self._validate_group(group)
             inst = self._groups.get(group) or self._GROUP_CLASSES[group](allow_jit=False)
-            inst.load_precompiled(path)
+            inst.load_precompiled(path, metadata_path)
             self._groups[group] = inst
         return self
 
