@@ -9,6 +9,8 @@ Tolerances (floating point, written here as the bar demands):
   * vs the reference test oracle (P rounded to the input dtype):
     max_err < 1e-2 or max_err/max|ref| < 1e-2
 """
+import os
+
 import numpy as np
 import pytest
 import torch
@@ -267,6 +269,32 @@ def test_torch_compile_uses_fake_impl():
     eager = f(q, k, v, m)
     compiled = torch.compile(f, backend="aot_eager", fullgraph=True)(q, k, v, m)
     assert torch.equal(eager, compiled)
+
+
+def test_aot_inductor_round_trip(tmp_path, monkeypatch):
+    """export -> AOTInductor package -> load -> run: the operator survives as a call into the
+    loaded library (traced through its fake implementation) and gives the eager result."""
+    from custom_ops_b200 import ops
+    ops.ensure_loaded("fa")
+    import torch._inductor.config as inductor_config
+    if os.path.exists("/usr/bin/g++"):                   # a host compiler with its OpenMP spec file
+        monkeypatch.setenv("CXX", "/usr/bin/g++")
+        monkeypatch.setattr(inductor_config.cpp, "cxx", ("/usr/bin/g++",))
+    q, k, v, m = _cuda(*make_case(2, 4, 2, 200, 333, 64, torch.bfloat16, "drop_bias", seed=3))
+
+    class Block(torch.nn.Module):
+        def forward(self, q, k, v, m):
+            return torch.ops.recsys_ops.mha_fwd_with_mask(q * 1.0, k, v, m) + 0.0
+
+    eager = ops.mha_fwd_with_mask(q, k, v, m)
+    exported = torch.export.export(Block(), (q, k, v, m))
+    assert any(n.target is torch.ops.recsys_ops.mha_fwd_with_mask.default for n in exported.graph.nodes
+               if n.op == "call_function")
+    package = torch._inductor.aoti_compile_and_package(exported, package_path=str(tmp_path / "block.pt2"))
+    runner = torch._inductor.aoti_load_package(package)
+    out = runner(q, k, v, m)
+    torch.cuda.synchronize()
+    assert torch.equal(out, eager)
 
 
 def test_cabi_rejects_bad_arguments_on_device():
