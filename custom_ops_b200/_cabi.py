@@ -28,6 +28,7 @@ EXPORTS = [
     "fa_mask_fwd_sm100_workspace_bytes",
     "fa_mask_fwd_sm100",
     "fa_mask_fwd_sm100_static_scratch",
+    "fa_mask_build_sm100",
     "fa_mask_fwd_sm100_combine",
     "fa_mask_fwd_sm100_device_status",
     "fa_mask_fwd_sm100_launch_count",
@@ -122,6 +123,10 @@ def load(path: str | None = None):
         ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int32,
         ctypes.c_int64, ctypes.c_int32, ctypes.c_int32, ctypes.c_int32, ctypes.c_int32,
         ctypes.c_void_p]
+    lib.fa_mask_build_sm100.restype = ctypes.c_int
+    lib.fa_mask_build_sm100.argtypes = [
+        ctypes.c_void_p, ctypes.c_int32, ctypes.c_int32, ctypes.c_int32, ctypes.c_int32, ctypes.c_int32,
+        ctypes.c_int32, ctypes.c_int32, ctypes.c_void_p, ctypes.c_int32, ctypes.c_void_p]
     lib.fa_mask_fwd_sm100_device_status.restype = ctypes.c_int
     lib.fa_mask_fwd_sm100_device_status.argtypes = [ctypes.c_int32, P(ctypes.c_uint32),
                                                     ctypes.c_int32]
@@ -203,6 +208,12 @@ def combine(o_parts: int, lse_parts: int, out: int, lse_out: int, num_parts: int
     check(load().fa_mask_fwd_sm100_combine(o_parts or None, lse_parts or None, out or None,
                                            lse_out or None, num_parts, rows, head_dim, dtype,
                                            out_fp32, device, stream or None))
+
+
+def build_mask(mask: int, batch: int, seqlen_q: int, seqlen_k: int, pitch: int, dtype: int, causal: int,
+               window: int, valid_lens: int, device: int, stream: int):
+    check(load().fa_mask_build_sm100(mask or None, batch, seqlen_q, seqlen_k, pitch, dtype, causal, window,
+                                     valid_lens or None, device, stream or None))
 
 
 def device_status(device: int = 0, clear: bool = True) -> int:

@@ -1432,6 +1432,38 @@ fa_mask_repitch_kernel(const uint16_t* __restrict__ src, uint16_t* __restrict__ 
 }
 
 // ---------------------------------------------------------------------------------
+// Mask from rules (padding / causal / sliding window): one 16-byte vector per thread.
+// ---------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256)
+fa_mask_build_kernel(uint16_t* __restrict__ mask, int Sq, int Sk, int pitch, uint32_t neg_inf16, int causal,
+                     int window, const int* __restrict__ valid_lens) {
+    const long long r = blockIdx.x;                   // b * Sq + i
+    const int b = static_cast<int>(r / Sq);
+    const int i = static_cast<int>(r % Sq);
+    const int limit = valid_lens != nullptr ? min(Sk, valid_lens[b]) : Sk;
+    const int diag = i + Sk - Sq;                     // last key a causal query sees
+    const int hi = causal ? min(limit - 1, diag) : limit - 1;          // visible keys: (lo, hi]
+    const int lo = window > 0 ? diag - window : -1;
+    const int c = (blockIdx.y * blockDim.x + threadIdx.x) * 8;
+    if (c >= pitch) return;
+    uint16_t* dst = mask + r * pitch + c;
+    uint32_t w[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        const int j0 = c + 2 * k, j1 = j0 + 1;
+        const uint32_t e0 = (j0 > lo && j0 <= hi) ? 0u : neg_inf16;
+        const uint32_t e1 = (j1 > lo && j1 <= hi) ? 0u : neg_inf16;
+        w[k] = e0 | (e1 << 16);
+    }
+    if (c + 8 <= pitch && (reinterpret_cast<uintptr_t>(dst) & 15u) == 0) {
+        *reinterpret_cast<uint4*>(dst) = make_uint4(w[0], w[1], w[2], w[3]);
+    } else {
+        for (int e = 0; e < 8 && c + e < pitch; ++e)
+            dst[e] = static_cast<uint16_t>(w[e >> 1] >> ((e & 1) * 16));
+    }
+}
+
+// ---------------------------------------------------------------------------------
 // Host side
 // ---------------------------------------------------------------------------------
 constexpr int kMaxDevices = 64;
@@ -2166,6 +2198,31 @@ int fa_mask_fwd_sm100_device_status(int32_t device, uint32_t* status, int32_t cl
         }
     }
     return v == 0 ? FA_SM100_OK : FA_SM100_ERR_DEVICE_WAIT;
+}
+
+int fa_mask_build_sm100(void* mask, int32_t batch, int32_t seqlen_q, int32_t seqlen_k, int32_t pitch,
+                        int32_t dtype, int32_t causal, int32_t window, const int32_t* valid_lens,
+                        int32_t device, void* stream) {
+    if (mask == nullptr) return FA_SM100_ERR_NULL;
+    if (dtype != FA_SM100_FP16 && dtype != FA_SM100_BF16) return FA_SM100_ERR_DTYPE;
+    if (batch < 0 || seqlen_q < 0 || seqlen_k < 0 || pitch < seqlen_k || device < 0 ||
+        device >= fa_sm100::kMaxDevices)
+        return FA_SM100_ERR_SHAPE;
+    if ((reinterpret_cast<uintptr_t>(mask) & 1u) != 0) return FA_SM100_ERR_ALIGN;
+    const long long rows = static_cast<long long>(batch) * seqlen_q;
+    if (rows == 0 || pitch == 0) return FA_SM100_OK;
+    if (rows > 0x7fffffffLL) return FA_SM100_ERR_SHAPE;
+    fa_sm100::DeviceGuard guard(device);
+    if (guard.err != cudaSuccess) return fa_sm100::cuda_failed(__LINE__);
+    const unsigned vec_blocks = static_cast<unsigned>((pitch + 8 * 256 - 1) / (8 * 256));
+    if (vec_blocks > 65535u) return FA_SM100_ERR_SHAPE;
+    const uint32_t neg = dtype == FA_SM100_BF16 ? 0xFF80u : 0xFC00u;
+    fa_sm100::fa_mask_build_kernel<<<dim3(static_cast<unsigned>(rows), vec_blocks), 256, 0,
+                                     static_cast<cudaStream_t>(stream)>>>(
+        static_cast<uint16_t*>(mask), seqlen_q, seqlen_k, pitch, neg, causal, window, valid_lens);
+    if (cudaPeekAtLastError() != cudaSuccess) return fa_sm100::cuda_failed(__LINE__);
+    ++fa_sm100::g_launches;
+    return FA_SM100_OK;
 }
 
 int fa_mask_fwd_sm100_static_scratch(const FaMaskFwdArgs* args, void* stream) {

@@ -162,6 +162,22 @@ int fa_mask_fwd_sm100(const FaMaskFwdArgs* args, void* workspace, size_t workspa
  * nothing in it has to start at zero. */
 int fa_mask_fwd_sm100_static_scratch(const FaMaskFwdArgs* args, void* stream);
 
+/* Writes an additive mask (0 visible, -inf masked) of shape (batch, 1, seqlen_q, pitch) straight
+ * into device memory from the rules callers of the operator otherwise spell out with a handful
+ * of tensor operations (the reference's recipes, examples/custom_mask_demo.py:33-65; there is no
+ * counterpart in the reference's operator interface).  Key j is visible to query i of batch b when
+ *     j < seqlen_k
+ *     and (valid_lens == NULL or j < valid_lens[b])                      padding
+ *     and (causal == 0 or j <= i + seqlen_k - seqlen_q)                  causal, right-aligned
+ *     and (window <= 0 or j > i + seqlen_k - seqlen_q - window)          sliding window
+ * `pitch` >= seqlen_k is the row length in elements; a multiple of 8 keeps every row 16-byte
+ * aligned, so the forward reads the mask in place however ragged seqlen_k is (pass it as
+ * mask_seqlen_k = mask_row_stride = pitch).  Columns >= seqlen_k are written as -inf.
+ * `valid_lens` is a device pointer to `batch` int32 values, or NULL. */
+int fa_mask_build_sm100(void* mask, int32_t batch, int32_t seqlen_q, int32_t seqlen_k, int32_t pitch,
+                        int32_t dtype, int32_t causal, int32_t window, const int32_t* valid_lens,
+                        int32_t device, void* stream);
+
 /* Merges `num_parts` normalised fp32 partial results that cover disjoint key
  * ranges: out = sum_s exp(lse_s - max) * o_s / sum_s exp(lse_s - max), rows whose
  * every lse is -inf give 0.  `o_parts` is (num_parts, rows, head_dim) fp32,

@@ -466,3 +466,43 @@ def test_host_memory_entry_point_matches_the_operator(chunk):
     with pytest.raises(ValueError):
         mha_fwd_with_mask_from_host(qp.cuda(), kp, vp, mp)
 
+
+# ---------------------------------------------------------------- masks from rules
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("case", [(2, 512, 512, dict(causal=True)),
+                                  (2, 300, 517, dict(causal=True, window=64)),
+                                  (3, 129, 1000, dict(valid_lens=[1000, 333, 0])),
+                                  (2, 64, 4099, dict(causal=True, window=700, valid_lens=[4099, 2500])),
+                                  (1, 50, 7, dict())])
+def test_rule_mask_equals_the_tensor_recipes(dtype, case):
+    """One kernel writes what the reference's recipes build with tensor operations
+    (examples/custom_mask_demo.py:33-65), bit for bit, at a pitch the forward reads in place."""
+    from custom_ops_b200 import ops
+    from custom_ops_b200.masks import rule_mask
+    b, sq, sk, rules = case
+    lens = rules.get("valid_lens")
+    m = rule_mask(b, sq, sk, dtype=dtype, causal=rules.get("causal", False), window=rules.get("window", 0),
+                  valid_lens=None if lens is None else torch.tensor(lens))
+    pitch = -(-sk // 8) * 8
+    assert m.shape == (b, 1, sq, pitch) and m.is_contiguous()
+    i = torch.arange(sq, device="cuda").view(sq, 1)
+    j = torch.arange(sk, device="cuda").view(1, sk)
+    vis = torch.ones(b, sq, sk, dtype=torch.bool, device="cuda")
+    if rules.get("causal"):
+        vis &= (j <= i + (sk - sq))
+    if rules.get("window", 0) > 0:
+        vis &= (j > i + (sk - sq) - rules["window"])
+    if lens is not None:
+        vis &= (j.view(1, 1, sk) < torch.tensor(lens, device="cuda").view(b, 1, 1))
+    ref = torch.zeros(b, 1, sq, sk, device="cuda", dtype=dtype).masked_fill(~vis.view(b, 1, sq, sk), float("-inf"))
+    assert torch.equal(m[..., :sk], ref)
+    assert torch.all(torch.isneginf(m[..., sk:]))
+    # and the operator takes it as it is: same result as with the materialised mask, no re-pitch
+    q, k, v, _ = make_case(b, 4, 2, sq, sk, 64, dtype, "zero", seed=41)
+    q, k, v = _cuda(q, k, v)
+    args = _cabi.make_args(batch=b, heads=4, heads_k=2, seqlen_q=sq, seqlen_k=sk, head_dim=64,
+                           dtype=_cabi.BF16 if dtype == torch.bfloat16 else _cabi.FP16,
+                           mask_seqlen_q=sq, mask_seqlen_k=pitch)
+    assert _cabi.plan(args).mask_repitched == 0
+    assert torch.equal(ops.mha_fwd_with_mask(q, k, v, m), ops.mha_fwd_with_mask(q, k, v, ref.contiguous()))
+

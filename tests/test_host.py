@@ -18,7 +18,7 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 # ------------------------------------------------------------------ C ABI
 def test_library_exports_every_declared_symbol():
     header = open(os.path.join(ROOT, "include", "fa_mask_fwd_sm100.h")).read()
-    declared = set(re.findall(r"\b(fa_mask_fwd_sm100\w*)\s*\(", header))
+    declared = set(re.findall(r"^(?:int|const char\*)\s+(fa_mask_\w+)\s*\(", header, flags=re.M))
     assert declared == set(_cabi.EXPORTS)
     lib = _cabi.load()
     for name in declared:
@@ -231,4 +231,22 @@ def test_host_memory_entry_point_checks_its_arguments():
     if not torch.cuda.is_available():
         with pytest.raises(RuntimeError):
             mha_fwd_with_mask_from_host(q, k, k, m)
+
+
+def test_rule_mask_checks_its_arguments():
+    from custom_ops_b200.masks import rule_mask
+    with pytest.raises(ValueError):
+        rule_mask(1, 8, 8, dtype=torch.float32)
+    with pytest.raises(ValueError):
+        rule_mask(1, 8, -1)
+    lib = _cabi.load()
+    assert lib.fa_mask_build_sm100(None, 1, 8, 8, 8, _cabi.BF16, 0, 0, None, 0, None) == -1
+    buf = (ctypes.c_uint8 * 64)()
+    addr = ctypes.addressof(buf)
+    assert lib.fa_mask_build_sm100(addr, 1, 8, 8, 4, _cabi.BF16, 0, 0, None, 0, None) == -3     # pitch < Sk
+    assert lib.fa_mask_build_sm100(addr, 1, 8, 8, 8, 7, 0, 0, None, 0, None) == -2              # dtype
+    assert lib.fa_mask_build_sm100(addr, 0, 8, 8, 8, _cabi.BF16, 0, 0, None, 0, None) == 0      # nothing to write
+    if not torch.cuda.is_available():
+        with pytest.raises(RuntimeError):
+            rule_mask(1, 8, 8)
 
