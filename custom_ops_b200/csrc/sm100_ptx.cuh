@@ -66,9 +66,12 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
     return ok != 0;
 }
 
-// Upper bound of one wait, in SM clock cycles (about 0.1 s): far above any legitimate
-// wait in these kernels, short enough that a broken launch drains in seconds.
-constexpr long long kMaxWaitCycles = 200000000LL;
+// Upper bound of one wait, in SM clock cycles (about a second).  The longest legitimate wait
+// in the persistent kernel lasts one whole unit of work (the scheduler warp waits for a unit
+// board to be released): about 2.5 us per 128 keys, so a second covers single-pass units of
+// tens of millions of keys, and a broken launch still drains in about that time - every CTA
+// runs into its own limit in parallel and CTAs that start later leave at once.
+constexpr long long kMaxWaitCycles = 2000000000LL;
 constexpr uint32_t kMaxPolls = 1u << 16;     // cap for the drain loops that have no clock check
 
 // Bounded wait.  `abort_saddr` is the shared-space address of a CTA-shared word: once any
