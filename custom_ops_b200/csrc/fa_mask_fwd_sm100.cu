@@ -294,6 +294,71 @@ fa_mask_fwd_kernel(const __grid_constant__ CUtensorMap tm_q,
     const int ring_slots = dual ? NS + 1 : NS;
     constexpr int kUnitConsumers = 3 + 8;   // two producers, MMA thread, lane 0 of each softmax warp
 
+    // Decode of a unit and its publication on board k & 1 (scheduler warp, all lanes; see the
+    // unit-scheduler role below).  The board is plain shared memory: the first unit of a CTA -
+    // always unit blockIdx.x, whole - is decoded before the set-up barrier, under the tensor
+    // memory allocation and the mbarrier initialisation of the other warps, and only its
+    // arrival on the "full" mbarrier waits for that barrier.  (Not with a skip list: the block
+    // flags are only valid once the pre-pass kernel has finished.)
+    auto publish_unit = [&](int k, int unit, int part, int part_begin, int part_n, int peer_last) {
+        int rest = unit;
+        const int sgroup = rest % p.split_groups;
+        rest /= p.split_groups;
+        // later query pairs first: under causal-like masks they carry the most key blocks
+        const int mpair = p.m_pairs - 1 - (rest % p.m_pairs);
+        rest /= p.m_pairs;
+        const int h = rest % p.H;
+        const int b = rest / p.H;
+        int count = 0;
+        if constexpr (LIST) {
+            const unsigned char* fl = p.block_flags +
+                (static_cast<long long>(b) * p.m_pairs + mpair) * p.kv_blocks;
+            const uint32_t lst = blk_list + (k & 1) * (kMaxListBlocks * 2);
+            for (int base_j = 0; base_j < p.kv_blocks; base_j += 32) {
+                const int jj = base_j + lane;
+                const bool need = jj < p.kv_blocks && fl[jj] != 0;
+                const unsigned ballot = __ballot_sync(0xffffffffu, need);
+                if (need) sts16(lst + 2 * (count + __popc(ballot & ((1u << lane) - 1u))), static_cast<uint32_t>(jj));
+                count += __popc(ballot);
+            }
+        }
+        const uint32_t ui = unit_board + (k & 1) * (kUiInts * 4);
+        if (lane < 2) {
+            // lane t describes slot t
+            const int t = lane;
+            const int m0 = mpair * (2 * kBlockM);
+            const int split = dual ? 2 * sgroup + t : sgroup;
+            // split s owns key blocks [s*nb/S, (s+1)*nb/S): sizes differ by at most one block
+            const unsigned nb = static_cast<unsigned>(p.kv_blocks), ns = static_cast<unsigned>(p.num_splits);
+            // (32 bits hold split * nb: at most 128 splits of at most 2^24 blocks)
+            int begin = static_cast<int>(static_cast<unsigned>(split) * nb / ns);
+            int end = static_cast<int>(static_cast<unsigned>(split + 1) * nb / ns);
+            if (part != kPartWhole) {          // single pass, cut at a CTA boundary
+                begin = part_begin;
+                end = part_begin + part_n;
+            }
+            const int row0 = dual ? m0 : m0 + t * kBlockM;
+            const bool on = dual ? (split < p.num_splits) : (row0 < p.Sq);
+            int n = on ? max(end - begin, 0) : -1;                 // -1: the slot does not exist
+            if (LIST && on) n = count;                             // may be 0: nothing visible at all
+            sts32(ui + 4 * (kUiSlot + 4 * t + kUiSplit), static_cast<uint32_t>(split));
+            sts32(ui + 4 * (kUiSlot + 4 * t + kUiBegin), static_cast<uint32_t>(begin));
+            sts32(ui + 4 * (kUiSlot + 4 * t + kUiN), static_cast<uint32_t>(n));
+            sts32(ui + 4 * (kUiSlot + 4 * t + kUiRow0), static_cast<uint32_t>(row0));
+            if (t == 0) {
+                sts32(ui + 4 * (kUiUnit), static_cast<uint32_t>(unit));
+                sts32(ui + 4 * (kUiPart), static_cast<uint32_t>(part));
+                sts32(ui + 4 * (kUiPeerLast), static_cast<uint32_t>(peer_last));
+                sts32(ui + 4 * (kUiB), static_cast<uint32_t>(b));
+                sts32(ui + 4 * (kUiH), static_cast<uint32_t>(h));
+                sts32(ui + 4 * (kUiSgroup), static_cast<uint32_t>(sgroup));
+                sts32(ui + 4 * (kUiKvPlane), static_cast<uint32_t>(b * p.Hk + h / (p.H / p.Hk)));
+                sts32(ui + 4 * (kUiQPlane), static_cast<uint32_t>(b * p.H + h));
+            }
+        }
+    };
+    if (!LIST && warp == 11) publish_unit(0, static_cast<int>(blockIdx.x), kPartWhole, 0, p.kv_blocks, 0);
+
     if (warp == kTmaWarp && lane == 0) {
         for (int t = 0; t < 2; ++t) {
             mbar_init(bar_q_full + 8 * t, 1);
@@ -545,61 +610,7 @@ fa_mask_fwd_kernel(const __grid_constant__ CUtensorMap tm_q,
                     }
                     break;
                 }
-                int rest = unit;
-                const int sgroup = rest % p.split_groups;
-                rest /= p.split_groups;
-                // later query pairs first: under causal-like masks they carry the most key blocks
-                const int mpair = p.m_pairs - 1 - (rest % p.m_pairs);
-                rest /= p.m_pairs;
-                const int h = rest % p.H;
-                const int b = rest / p.H;
-                int count = 0;
-                if constexpr (LIST) {
-                    const unsigned char* fl = p.block_flags +
-                        (static_cast<long long>(b) * p.m_pairs + mpair) * p.kv_blocks;
-                    const uint32_t lst = blk_list + (k & 1) * (kMaxListBlocks * 2);
-                    for (int base_j = 0; base_j < p.kv_blocks; base_j += 32) {
-                        const int jj = base_j + lane;
-                        const bool need = jj < p.kv_blocks && fl[jj] != 0;
-                        const unsigned ballot = __ballot_sync(0xffffffffu, need);
-                        if (need) sts16(lst + 2 * (count + __popc(ballot & ((1u << lane) - 1u))), static_cast<uint32_t>(jj));
-                        count += __popc(ballot);
-                    }
-                }
-                const uint32_t ui = unit_board + (k & 1) * (kUiInts * 4);
-                if (lane < 2) {
-                    // lane t describes slot t
-                    const int t = lane;
-                    const int m0 = mpair * (2 * kBlockM);
-                    const int split = dual ? 2 * sgroup + t : sgroup;
-                    // split s owns key blocks [s*nb/S, (s+1)*nb/S): sizes differ by at most one block
-                    const unsigned nb = static_cast<unsigned>(p.kv_blocks), ns = static_cast<unsigned>(p.num_splits);
-                    // (32 bits hold split * nb: at most 128 splits of at most 2^24 blocks)
-                    int begin = static_cast<int>(static_cast<unsigned>(split) * nb / ns);
-                    int end = static_cast<int>(static_cast<unsigned>(split + 1) * nb / ns);
-                    if (part != kPartWhole) {          // single pass, cut at a CTA boundary
-                        begin = part_begin;
-                        end = part_begin + part_n;
-                    }
-                    const int row0 = dual ? m0 : m0 + t * kBlockM;
-                    const bool on = dual ? (split < p.num_splits) : (row0 < p.Sq);
-                    int n = on ? max(end - begin, 0) : -1;                 // -1: the slot does not exist
-                    if (LIST && on) n = count;                             // may be 0: nothing visible at all
-                    sts32(ui + 4 * (kUiSlot + 4 * t + kUiSplit), static_cast<uint32_t>(split));
-                    sts32(ui + 4 * (kUiSlot + 4 * t + kUiBegin), static_cast<uint32_t>(begin));
-                    sts32(ui + 4 * (kUiSlot + 4 * t + kUiN), static_cast<uint32_t>(n));
-                    sts32(ui + 4 * (kUiSlot + 4 * t + kUiRow0), static_cast<uint32_t>(row0));
-                    if (t == 0) {
-                        sts32(ui + 4 * (kUiUnit), static_cast<uint32_t>(unit));
-                        sts32(ui + 4 * (kUiPart), static_cast<uint32_t>(part));
-                        sts32(ui + 4 * (kUiPeerLast), static_cast<uint32_t>(peer_last));
-                        sts32(ui + 4 * (kUiB), static_cast<uint32_t>(b));
-                        sts32(ui + 4 * (kUiH), static_cast<uint32_t>(h));
-                        sts32(ui + 4 * (kUiSgroup), static_cast<uint32_t>(sgroup));
-                        sts32(ui + 4 * (kUiKvPlane), static_cast<uint32_t>(b * p.Hk + h / (p.H / p.Hk)));
-                        sts32(ui + 4 * (kUiQPlane), static_cast<uint32_t>(b * p.H + h));
-                    }
-                }
+                if (LIST || k > 0) publish_unit(k, unit, part, part_begin, part_n, peer_last);
                 __syncwarp();
                 if (lane == 0) mbar_arrive(bar_unit_full + 8 * (k & 1));    // release: board and list visible
             }
