@@ -1665,13 +1665,17 @@ static int make_plan(const FaMaskFwdArgs* a, FaMaskFwdPlan* plan) {
                        (a->disable & FA_SM100_NO_TILE_SKIP) == 0) ? 1 : 0;
     // (block flags, then the counter the attention kernel hands out its units from)
     if (plan->tile_skip) ws += align256(static_cast<size_t>(a->batch) * m_pairs * nb) + 256;
-    // More single-pass units than CTAs: the CTAs take equal shares of all (unit, key block)
-    // steps and a unit cut at a share boundary is merged through a per-CTA slot of scratch.
+    // More single-pass units than CTAs and a last round that is at most half full: its units
+    // are done in P pieces by P CTAs each.  A piece costs an epilogue of its own and the first
+    // piece about 1.5 key blocks' time per partial it merges (measured), so the piece count
+    // that pays is about sqrt(0.65 nb), and below six key blocks none does.
     plan->unit_cut = 0;
-    if (!dual && splits == 1 && units > dev->sm_count && units % dev->sm_count != 0 &&
+    if (!dual && splits == 1 && nb >= 6 && units > dev->sm_count && units % dev->sm_count != 0 &&
         (a->disable & FA_SM100_NO_UNIT_CUT) == 0) {
         long long pieces = dev->sm_count / (units % dev->sm_count);
-        if (pieces > nb) pieces = nb;
+        long long best = 2;
+        while ((best + 1) * (best + 1) * 100 <= 65LL * nb) ++best;     // floor(sqrt(0.65 nb)), at least 2
+        if (pieces > best) pieces = best;
         if (pieces >= 2) plan->unit_cut = static_cast<int32_t>(pieces);
     }
     if (plan->unit_cut) ws += cut_bytes(plan->grid_x, d);

@@ -112,7 +112,7 @@ typedef struct FaMaskFwdPlan {
                                  * launcher drops the pre-pass for a while after it found nothing to
                                  * skip twice in a row for the same mask buffer and shape. */
     int32_t unit_cut;           /* P >= 2: there are more single-pass units than CTAs and the R units
-                                 * of the last, partial round are done by P = SMs / R CTAs each (one
+                                 * of the last, partial round are done by P <= SMs / R CTAs each (one
                                  * piece of the key blocks per CTA, merged through the workspace)
                                  * instead of leaving most SMs idle; 0: every unit is done by one CTA */
     uint64_t workspace_bytes;

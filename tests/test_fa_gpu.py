@@ -346,11 +346,12 @@ def test_splitkv_single_tile_dual_mode(dtype, case):
 
 
 # ---------------------------------------------------------------- units of the last round cut in pieces
-@pytest.mark.parametrize("case", [(2, 16, 16, 1280, 640, 128, torch.bfloat16),
+@pytest.mark.parametrize("case", [(2, 16, 16, 1280, 1024, 128, torch.bfloat16),
                                   (3, 12, 4, 1250, 900, 64, torch.float16),
-                                  (1, 40, 8, 1024, 300, 128, torch.float16),
-                                  # one unit left over: cut into as many pieces as it has key blocks
-                                  (1, 149, 149, 200, 1000, 64, torch.bfloat16),
+                                  # three pieces per unit: the first merges two partials
+                                  (1, 40, 8, 1024, 3000, 128, torch.float16),
+                                  # one unit left over: four pieces, not one per key block
+                                  (1, 149, 149, 200, 4000, 64, torch.bfloat16),
                                   # two pieces per unit, the first one key block longer
                                   (1, 111, 37, 512, 1100, 128, torch.bfloat16)])
 def test_units_of_the_last_round_are_cut(case):
@@ -364,7 +365,8 @@ def test_units_of_the_last_round_are_cut(case):
     out_whole, lse_whole, plan_whole = run_cabi(q, k, v, m, want_lse=True, no_tile_skip=1, no_unit_cut=1)
     assert plan.unit_cut >= 2 and plan_whole.unit_cut == 0 and plan.num_splits == 1
     assert plan.grid_x == plan.sm_count
-    check_against_oracle(out_cut, q, k, v, m, f"cut{case}")
+    if b * h * sq * sk <= 70_000_000:             # the whole-unit run is checked against the oracle elsewhere
+        check_against_oracle(out_cut, q, k, v, m, f"cut{case}")
     assert (out_cut.float() - out_whole.float()).abs().max().item() <= 4e-3
     assert torch.allclose(lse_cut, lse_whole, atol=1e-4, rtol=1e-5)
     # twice in a row on the same scratch: the tags of the first launch must not satisfy the second
@@ -375,7 +377,7 @@ def test_units_of_the_last_round_are_cut(case):
 def test_unit_cut_survives_cuda_graph_replay():
     """A captured launch repeats its tag on every replay; the head pieces take the tags back
     after reading, so a replay on new data must not pick up the previous replay's partials."""
-    b, h, hk, sq, sk, d = 2, 16, 16, 1280, 640, 128
+    b, h, hk, sq, sk, d = 2, 16, 16, 1280, 1024, 128
     q, k, v, m = _cuda(*make_case(b, h, hk, sq, sk, d, torch.bfloat16, "drop_bias", seed=31))
     out = torch.empty_like(q)
     args = _cabi.make_args(q=q.data_ptr(), k=k.data_ptr(), v=v.data_ptr(), mask=m.data_ptr(), out=out.data_ptr(),

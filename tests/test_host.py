@@ -52,7 +52,7 @@ def test_plan_of_the_five_configurations():
     assert (p.num_splits, p.kv_blocks, p.grid_x, p.q_tiles_per_cta) == (1, 16, min(512, sm), 2)
     # block flags (4 * 8 * 16 bytes -> 512) + the unit counter; more units than CTAs: the units of
     # the last, partial round are cut in pieces, which takes per CTA 256 rows of fp32 O + LSE and 8 tags
-    pieces = min(sm // (512 % sm), 16) if 512 > sm and 512 % sm else 0     # CTAs per unit of the last round
+    pieces = min(sm // (512 % sm), 3) if 512 > sm and 512 % sm else 0      # CTAs per unit of the last round (at most floor(sqrt(0.65 * 16)))
     pieces = pieces if pieces >= 2 else 0
     cut = -(-(p.grid_x * 256 * (128 + 1) * 4 + p.grid_x * 8 * 8) // 256) * 256 if pieces else 0
     assert p.unit_cut == pieces
@@ -249,4 +249,21 @@ def test_rule_mask_checks_its_arguments():
     if not torch.cuda.is_available():
         with pytest.raises(RuntimeError):
             rule_mask(1, 8, 8)
+
+
+def test_plan_unit_cut_rule():
+    """Pieces per unit of a last round that is at most half full: SMs / left-over units, at most
+    floor(sqrt(0.65 * key blocks)) (every further piece costs the first one a merge), none below
+    six key blocks, none when the rounds are whole or the caller switches it off."""
+    sm = _plan().sm_count
+    def cut(units, sk, **kw):
+        return _plan(batch=1, heads=units, heads_k=units, seqlen_q=256, seqlen_k=sk, **kw).unit_cut
+    assert cut(sm + 1, 128 * 16) == 3
+    assert cut(sm + 1, 128 * 64) == 6
+    assert cut(sm + sm // 2, 128 * 64) == 2
+    assert cut(sm + sm // 2 + 1, 128 * 64) == 0          # more than half a round left over
+    assert cut(2 * sm, 128 * 16) == 0                    # whole rounds only
+    assert cut(sm + 1, 128 * 5) == 0                     # too few key blocks to pay
+    assert cut(sm + 1, 128 * 16, no_unit_cut=1) == 0
+    assert cut(sm - 1, 128 * 16) == 0                    # fewer units than SMs: nothing to cut
 
