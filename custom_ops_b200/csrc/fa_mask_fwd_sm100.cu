@@ -821,7 +821,14 @@ fa_mask_fwd_kernel(const __grid_constant__ CUtensorMap tm_q,
                 const bool tail = (col0 + kBlockN) > p.Sk;
                 const uint32_t par = gstep & 1;
 
-                bool ok = mbar_wait(bar_s, par, abort_flag, p.status, kStSoftmaxS);
+                // The mask panels of this step were requested a whole step ago.  Their barriers
+                // are tested first, while the scores are still being computed: a barrier test
+                // costs about 150 cycles even when the barrier has long completed, and here that
+                // latency falls into time the thread would spend waiting anyway, so that nothing
+                // but the wake-up from the score barrier stands between S and the first load.
+                bool ok = mbar_wait(bar_m_full + 8 * (2 * t), par, abort_flag, p.status, kStSoftmaxMask);
+                ok = mbar_wait(bar_m_full + 8 * (2 * t + 1), par, abort_flag, p.status, kStSoftmaxMask) && ok;
+                ok = mbar_wait(bar_s, par, abort_flag, p.status, kStSoftmaxS) && ok;
                 if (!__all_sync(0xffffffffu, ok)) { alive = false; break; }
                 tc_fence_after();
 
@@ -832,9 +839,6 @@ fa_mask_fwd_kernel(const __grid_constant__ CUtensorMap tm_q,
                 float mt0 = -INFINITY, mt1 = -INFINITY;
 #pragma unroll
                 for (int pn = 0; pn < 2; ++pn) {
-                    ok = mbar_wait(bar_m_full + 8 * (2 * t + pn), par, abort_flag, p.status,
-                                   kStSoftmaxMask);
-                    if (!__all_sync(0xffffffffu, ok)) { alive = false; break; }
 #pragma unroll
                     for (int c = 0; c < 8; ++c) {
                         const uint4 mv = lds128(m_row_addr + pn * kPanelBytes +
@@ -857,7 +861,6 @@ fa_mask_fwd_kernel(const __grid_constant__ CUtensorMap tm_q,
                     }
                     mbar_arrive(bar_m_empty + 8 * (2 * t + pn));      // panel may be refilled
                 }
-                if (!alive) break;
                 if (tail) {
                     // Last key block of a ragged Sk: columns >= Sk are masked whatever the
                     // mask tile holds there.  Kept out of the main loop on purpose.
