@@ -68,10 +68,14 @@ def _host_cxx() -> str:
 
 
 def _fingerprint(paths, extra: str) -> str:
+    """Hash of the build inputs: flags, file names and contents -- not the directory the tree
+    happens to live in, so a tree that was built in one place and copied to another (with its
+    libraries and stamps) is still up to date there and is not rebuilt under a process that
+    already holds the old library."""
     h = hashlib.sha256(extra.encode())
     for p in paths:
         with open(p, "rb") as f:
-            h.update(p.encode() + b"\0" + f.read())
+            h.update(os.path.basename(p).encode() + b"\0" + f.read())
     return h.hexdigest()
 
 

@@ -134,6 +134,10 @@ struct KParams {
     int out_fp32;
     int wide_stores;          // 1: out and the partials are 32-byte aligned (256-bit stores)
     float scale;              // 1 / sqrt(d)
+    unsigned int wait_kcycles;   // limit of every bounded wait, in units of 1024 SM cycles
+    int mask_bcast;           // 1: one mask plane serves every batch element (batch stride 0)
+    int test_stall_mask;      // test only: the mask producer loads nothing, so the waits for the
+                              // mask run into their limit and the kernel reports it
 };
 
 template <bool BF16>
@@ -154,9 +158,11 @@ __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
 // Unit cutting.  With G CTAs and units of equal length, whole rounds of G units go to the
 // CTAs one unit each; the R < G units of a last, partial round would leave most SMs idle, so
 // with P = G / R >= 2 each of them is done by P consecutive CTAs, one piece of its key blocks
-// each.  Every piece but the first (kPartTail) ends in a normalised fp32 partial plus LSE in
-// the CTA's slot of the workspace; the first piece (kPartHead) merges the partials of the
-// other pieces into its own result.  (Equal shares of ALL steps, or of the last round's, were
+// each.  Every piece but the last (kPartTail) ends in a normalised fp32 partial plus LSE in
+// the CTA's slot of the workspace; the last piece (kPartHead), which the CTA with the highest
+// index of the group holds, merges the partials of the other pieces into its own result.  The
+// merging CTA is the one that is dispatched last: whatever it waits for was written by CTAs
+// that are already resident or finished, also when another kernel holds part of the GPU.  (Equal shares of ALL steps, or of the last round's, were
 // measured and lose: the partial traffic of 148 CTAs at once costs more than the idle SMs.)
 enum : int { kPartWhole = 0, kPartTail = 1, kPartHead = 2 };
 
@@ -167,7 +173,7 @@ enum : int {
     kUiB = 0, kUiH = 1, kUiSgroup = 2, kUiKvPlane = 3, kUiQPlane = 4,
     kUiUnit = 5,    // index of the unit; -1: no more work for this CTA
     kUiPart = 6,    // kPartWhole, kPartTail or kPartHead
-    kUiPeerLast = 7,  // kPartHead: the last CTA that holds a piece of this unit
+    kUiPeerLast = 7,  // kPartHead: the first CTA that holds a piece of this unit (they end at this one)
     kUiSlot = 8,
     kUiSplit = 0,   // KV split the slot covers
     kUiBegin = 1,   // first key block
@@ -268,6 +274,7 @@ fa_mask_fwd_kernel(const __grid_constant__ CUtensorMap tm_q,
     const uint32_t tmem_slot_addr = sBar + 320;        // tensor-memory base written by tcgen05.alloc
     const uint32_t abort_flag = sBar + 324;            // set once a bounded wait of this CTA gave up
     const uint32_t bail_word = sBar + 328;
+    const uint32_t wait_limit = sBar + 332;            // abort_flag + 8: limit of the bounded waits
     const uint32_t unit_board = sBar + 384;            // [2][kUiInts] ints
     const uint32_t blk_list = sBar + C::kBarBytes;     // [2][kMaxListBlocks] uint16
 
@@ -276,7 +283,10 @@ fa_mask_fwd_kernel(const __grid_constant__ CUtensorMap tm_q,
 
     // Once any CTA of any launch gave up on a wait, the status word stays set until
     // the host clears it; later CTAs leave at once so a broken launch drains quickly.
-    if (threadIdx.x == 0) sts32(bail_word, *reinterpret_cast<volatile unsigned int*>(p.status));
+    if (threadIdx.x == 0) {
+        sts32(bail_word, *reinterpret_cast<volatile unsigned int*>(p.status));
+        sts32(wait_limit, p.wait_kcycles);
+    }
     __syncthreads();
     if (lds32(bail_word) != 0) return;
 
@@ -495,7 +505,7 @@ fa_mask_fwd_kernel(const __grid_constant__ CUtensorMap tm_q,
                         bool done = false;
                         for (uint32_t it = 0; it < kMaxPolls && !done; ++it)
                             done = mbar_try_wait(bar_kv_full + 8 * r.slot, r.phase);
-                        if (!done) atomicMax(p.status, static_cast<unsigned int>(kStDrain));
+                        if (!done) report_gave_up(p.status, kStDrain);
                     }
                 }
             }
@@ -518,8 +528,8 @@ fa_mask_fwd_kernel(const __grid_constant__ CUtensorMap tm_q,
                     const int n_of[2] = {max(ui_get(ui, kUiSlot + kUiN), 0), max(ui_get(ui, kUiSlot + 4 + kUiN), 0)};
                     const int begin_of[2] = {ui_get(ui, kUiSlot + kUiBegin), ui_get(ui, kUiSlot + 4 + kUiBegin)};
                     const int row0_of[2] = {ui_get(ui, kUiSlot + kUiRow0), ui_get(ui, kUiSlot + 4 + kUiRow0)};
-                    const int b = ui_get(ui, kUiB);
-                    const int nmax = max(n_of[0], n_of[1]);
+                    const int b = p.mask_bcast ? 0 : ui_get(ui, kUiB);
+                    const int nmax = p.test_stall_mask ? 0 : max(n_of[0], n_of[1]);
                     for (int j = 0; ok && j < nmax; ++j) {
 #pragma unroll
                         for (int t = 0; t < 2; ++t) {
@@ -549,7 +559,7 @@ fa_mask_fwd_kernel(const __grid_constant__ CUtensorMap tm_q,
                         bool done = false;
                         for (uint32_t it = 0; it < kMaxPolls && !done; ++it)
                             done = mbar_try_wait(bar_m_full + 8 * i, ph[i] ^ 1u);
-                        if (!done) atomicMax(p.status, static_cast<unsigned int>(kStDrain));
+                        if (!done) report_gave_up(p.status, kStDrain);
                     }
                 }
             }
@@ -586,14 +596,15 @@ fa_mask_fwd_kernel(const __grid_constant__ CUtensorMap tm_q,
                         // CTAs c = u * P .. u * P + P - 1 share the u-th unit of the last round
                         const int piece = static_cast<int>(blockIdx.x) % p.cut_units;
                         unit = tail_unit;
-                        // The first piece is one key block longer than its share: the other
-                        // pieces' partials are then in memory by the time it wants them.
+                        // The last piece, the merging one, is one key block longer than its
+                        // share: the other pieces' partials are then in memory by the time it
+                        // wants them.
                         const int shift = p.kv_blocks >= 2 * p.cut_units ? 1 : 0;
-                        part_begin = piece == 0 ? 0 : piece * p.kv_blocks / p.cut_units + shift;
+                        part_begin = piece == 0 ? 0 : piece * p.kv_blocks / p.cut_units - shift;
                         part_n = (piece + 1 == p.cut_units ? p.kv_blocks
-                                                           : (piece + 1) * p.kv_blocks / p.cut_units + shift) - part_begin;
-                        part = piece == 0 ? kPartHead : kPartTail;
-                        peer_last = static_cast<int>(blockIdx.x) + p.cut_units - 1;
+                                                           : (piece + 1) * p.kv_blocks / p.cut_units - shift) - part_begin;
+                        part = piece + 1 == p.cut_units ? kPartHead : kPartTail;
+                        peer_last = static_cast<int>(blockIdx.x) - (p.cut_units - 1);
                     }
                 } else if (k > 0) {
                     if (LIST) {
@@ -1018,21 +1029,22 @@ fa_mask_fwd_kernel(const __grid_constant__ CUtensorMap tm_q,
                 float lse_val = dead ? -INFINITY : m_ref + __logf(l);
                 const int tile_row = t * kBlockM + row_in_tile;        // row inside the 256-row pair
                 if (part == kPartHead) {
-                    // The other pieces of this unit were done by the next CTAs, up to peer_last:
+                    // The other pieces of this unit were done by the CTAs before this one, from peer_last on:
                     // in each, the softmax warp with the same rows wrote a normalised partial
                     // and then its tag.
                     const long long lse_base = static_cast<long long>(gridDim.x) * (2 * kBlockM) * D;
                     const unsigned long long* tags = reinterpret_cast<const unsigned long long*>(
                         p.cut_part + static_cast<long long>(gridDim.x) * (2 * kBlockM) * (D + 1));
-                    for (int slot = static_cast<int>(blockIdx.x) + 1; slot <= peer_last; ++slot) {
+                    for (int slot = peer_last; slot < static_cast<int>(blockIdx.x); ++slot) {
                         bool ok = true;
                         if (lane == 0) {
                             const long long t0 = clock64();
                             while (ld_acquire_u64(tags + slot * 8 + warp) != p.cut_tag) {
-                                if (lds32(abort_flag) != 0u || clock64() - t0 > kMaxWaitCycles) {
+                                if (lds32(abort_flag) != 0u ||
+                                    ((clock64() - t0) >> 10) > static_cast<long long>(p.wait_kcycles)) {
                                     ok = false;
                                     sts32(abort_flag, 1u);
-                                    atomicMax(p.status, static_cast<unsigned int>(kStPartial));
+                                    report_gave_up(p.status, kStPartial);
                                     break;
                                 }
                             }
@@ -1489,6 +1501,8 @@ struct DeviceInfo {
     int sm_count = 0;
     int cc_major = 0;
     unsigned int* status_ptr = nullptr;
+    unsigned int* status_host = nullptr;     // pinned, mapped: the kernels' copy of a wait that gave up
+    bool status_host_failed = false;
     bool attr_set[8] = {false, false, false, false, false, false, false, false};
     bool queried = false;
 };
@@ -1541,6 +1555,10 @@ static int validate(const FaMaskFwdArgs* a) {
     if (a->heads > 65535 || a->batch > 65535) return FA_SM100_ERR_SHAPE;
     if (a->mask_seqlen_q < a->seqlen_q || a->mask_seqlen_k < a->seqlen_k) return FA_SM100_ERR_SHAPE;
     if (a->mask_row_stride < a->mask_seqlen_k || a->mask_batch_stride < 0) return FA_SM100_ERR_SHAPE;
+    // one mask plane for every batch element (stride 0) or planes that do not overlap
+    if (a->batch > 1 && a->mask_batch_stride != 0 &&
+        a->mask_batch_stride < static_cast<int64_t>(a->seqlen_q) * a->mask_row_stride)
+        return FA_SM100_ERR_SHAPE;
     if (a->num_splits < 0 || a->num_splits > FA_SM100_MAX_SPLITS) return FA_SM100_ERR_SPLITS;
     if (a->device < 0 || a->device >= kMaxDevices) return FA_SM100_ERR_SHAPE;
     return FA_SM100_OK;
@@ -1705,6 +1723,7 @@ static int encode_map(CUtensorMap* tm, const void* ptr, int dtype, int planes, i
     const cuuint64_t dims[3] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows),
                                 static_cast<cuuint64_t>(planes)};
     // A single plane still needs a legal (multiple of 16 bytes, non-zero) outer stride.
+    // (Callers pass planes = 1 for a mask whose one plane serves every batch element.)
     if (plane_pitch <= 0) plane_pitch = static_cast<long long>(rows) * row_pitch;
     const cuuint64_t strides[2] = {static_cast<cuuint64_t>(row_pitch) * 2,
                                    static_cast<cuuint64_t>(plane_pitch) * 2};
@@ -1755,7 +1774,7 @@ static int get_maps(const MapKey& key, CUtensorMap* tq, CUtensorMap* tk, CUtenso
     if ((rc = encode_map(tv, key.v, key.dtype, key.B * key.Hk, key.Sk, key.d, key.d,
                          static_cast<long long>(key.Sk) * key.d)) != FA_SM100_OK) return rc;
     // mask: (batch, Sq rows, Sk columns); reads beyond either extent return 0
-    if ((rc = encode_map(tm, key.mask, key.dtype, key.B, key.Sq, key.Sk, key.mask_rs,
+    if ((rc = encode_map(tm, key.mask, key.dtype, key.mask_bs == 0 ? 1 : key.B, key.Sq, key.Sk, key.mask_rs,
                          key.mask_bs)) != FA_SM100_OK) return rc;
     MapEntry& e = g_map_cache[g_map_next];
     g_map_next = (g_map_next + 1) % kMapCache;
@@ -1865,6 +1884,43 @@ static int status_pointer(DeviceInfo* dev) {
     return FA_SM100_OK;
 }
 
+// A bounded wait that runs out leaves the output partly unwritten; the device status word
+// records it, but reading that word means synchronising.  So the kernels also write the code
+// to one word of pinned host memory mapped into the device's address space, and every forward
+// looks at that word first - a plain host load, no synchronisation - and refuses to launch
+// while it is set (fa_mask_fwd_sm100_device_status clears both).  The call that saw the
+// timeout itself has already returned; it is the NEXT call that reports it.
+// Allocating the word is skipped while `stream` is being captured (an allocation would break
+// the capture) and where the caller must not allocate (`may_allocate` false).
+static std::mutex g_status_host_mutex;
+static void status_host_setup(DeviceInfo* dev, cudaStream_t stream, bool may_allocate) {
+    if (dev->status_host != nullptr || dev->status_host_failed || !may_allocate) return;
+    cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+    if (cudaStreamIsCapturing(stream, &cap) != cudaSuccess) {
+        cudaGetLastError();
+        return;
+    }
+    if (cap != cudaStreamCaptureStatusNone) return;
+    std::lock_guard<std::mutex> lock(g_status_host_mutex);
+    if (dev->status_host != nullptr || dev->status_host_failed) return;
+    void* ptr = nullptr;
+    if (cudaHostAlloc(&ptr, 64, cudaHostAllocMapped | cudaHostAllocPortable) != cudaSuccess) {
+        cudaGetLastError();
+        dev->status_host_failed = true;
+        return;
+    }
+    *static_cast<volatile unsigned int*>(ptr) = 0u;
+    void* dptr = nullptr;
+    if (cudaHostGetDevicePointer(&dptr, ptr, 0) != cudaSuccess ||
+        cudaMemcpyToSymbol(g_fa_status_host, &dptr, sizeof(dptr)) != cudaSuccess) {
+        cudaGetLastError();
+        cudaFreeHost(ptr);
+        dev->status_host_failed = true;
+        return;
+    }
+    dev->status_host = static_cast<unsigned int*>(ptr);
+}
+
 // ---------------------------------------------------------------------------------
 // Is the tile-skip pre-pass worth running for this mask?
 // ---------------------------------------------------------------------------------
@@ -1897,10 +1953,16 @@ static std::mutex g_hint_mutex;
 
 // Returns true when the pre-pass should run; *counter is where it should count (or NULL).
 static bool want_classify(const FaMaskFwdArgs* a, const void* mask, long long bs, long long rs,
-                          bool adaptive, int** counter) {
+                          bool adaptive, cudaStream_t stream, int** counter) {
     *counter = nullptr;
     if (!adaptive) return true;
     std::lock_guard<std::mutex> lock(g_hint_mutex);
+    if (g_hint_words == nullptr && !g_hint_failed) {
+        // no allocation inside a stream capture: the pre-pass then simply runs
+        cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+        if (cudaStreamIsCapturing(stream, &cap) != cudaSuccess) cudaGetLastError();
+        if (cap != cudaStreamCaptureStatusNone) return true;
+    }
     if (g_hint_words == nullptr && !g_hint_failed) {
         void* ptr = nullptr;
         if (cudaHostAlloc(&ptr, kHintSlots * sizeof(int), cudaHostAllocMapped | cudaHostAllocPortable) !=
@@ -1994,6 +2056,10 @@ static int forward(const FaMaskFwdArgs* a, void* workspace, size_t workspace_byt
 
     if ((rc = get_encode()) != FA_SM100_OK) return rc;
     if ((rc = status_pointer(dev)) != FA_SM100_OK) return rc;
+    // (adaptive_skip is false exactly for the entry point that must not allocate)
+    status_host_setup(dev, stream, /*may_allocate=*/adaptive_skip);
+    if (dev->status_host != nullptr && *static_cast<volatile unsigned int*>(dev->status_host) != 0u)
+        return FA_SM100_ERR_DEVICE_WAIT;
 
     // workspace carve-up: [o_part][lse_part][re-pitched mask]
     uint8_t* ws = static_cast<uint8_t*>(workspace);
@@ -2027,7 +2093,7 @@ static int forward(const FaMaskFwdArgs* a, void* workspace, size_t workspace_byt
     }
     int* hint_counter = nullptr;
     const bool run_classify = plan.tile_skip &&
-        want_classify(a, mask_ptr, mask_bs, mask_rs, adaptive_skip, &hint_counter);
+        want_classify(a, mask_ptr, mask_bs, mask_rs, adaptive_skip, stream, &hint_counter);
     if (run_classify) {
         unsigned char* flags = ws + (plan.mask_repitched
             ? align256(static_cast<size_t>(a->batch) * a->seqlen_q * ((a->seqlen_k + 7) & ~7) * 2) : 0);
@@ -2077,6 +2143,16 @@ static int forward(const FaMaskFwdArgs* a, void* workspace, size_t workspace_byt
     kp.out_fp32 = a->out_fp32;
     kp.wide_stores = (((reinterpret_cast<uintptr_t>(a->out) | reinterpret_cast<uintptr_t>(o_part)) & 31u) == 0) ? 1 : 0;
     kp.scale = static_cast<float>(1.0 / std::sqrt(static_cast<double>(d)));
+    kp.wait_kcycles = kMaxWaitKcycles;
+    kp.mask_bcast = (mask_bs == 0 && a->batch > 1) ? 1 : 0;
+    if (a->disable & FA_SM100_TEST_STALL_MASK) {
+        // test only: the mask never arrives, every wait gets a short limit (default 2 M cycles,
+        // about a millisecond), the kernel gives up cleanly and reports it
+        kp.test_stall_mask = 1;
+        const char* env = std::getenv("FA_SM100_TEST_WAIT_KCYCLES");
+        const long v = env != nullptr ? std::atol(env) : 0;
+        kp.wait_kcycles = v > 0 ? static_cast<unsigned int>(v) : 2000u;
+    }
 
     CUtensorMap tq, tk, tv, tm;
     MapKey key;
@@ -2215,6 +2291,8 @@ int fa_mask_fwd_sm100_device_status(int32_t device, uint32_t* status, int32_t cl
             return fa_sm100::cuda_failed(__LINE__);
         }
     }
+    if (clear && fa_sm100::g_dev[device].status_host != nullptr)
+        *static_cast<volatile unsigned int*>(fa_sm100::g_dev[device].status_host) = 0u;
     return v == 0 ? FA_SM100_OK : FA_SM100_ERR_DEVICE_WAIT;
 }
 

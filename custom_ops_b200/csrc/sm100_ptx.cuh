@@ -72,11 +72,27 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 // tens of millions of keys, and a broken launch still drains in about that time - every CTA
 // runs into its own limit in parallel and CTAs that start later leave at once.
 constexpr long long kMaxWaitCycles = 2000000000LL;
+constexpr uint32_t kMaxWaitKcycles = static_cast<uint32_t>(kMaxWaitCycles >> 10);
 constexpr uint32_t kMaxPolls = 1u << 16;     // cap for the drain loops that have no clock check
 
-// Bounded wait.  `abort_saddr` is the shared-space address of a CTA-shared word: once any
-// role of the CTA gave up, every other wait of that CTA returns at once so the CTA drains
-// and exits.  (A shared-space address costs one register where a generic pointer costs two.)
+// Where a wait that gave up reports, besides the device status word: a word of pinned host
+// memory mapped into the device's address space (NULL until the host has set one up), which
+// the host reads at the start of its next call without synchronising anything.
+__device__ unsigned int* g_fa_status_host = nullptr;
+
+__device__ __forceinline__ void report_gave_up(unsigned int* status, uint32_t code) {
+    atomicMax(status, code);
+    unsigned int* host_word = *reinterpret_cast<unsigned int* volatile*>(&g_fa_status_host);
+    if (host_word != nullptr) {
+        *reinterpret_cast<volatile unsigned int*>(host_word) = code;
+        __threadfence_system();
+    }
+}
+
+// Bounded wait.  `abort_saddr` is the shared-space address of two CTA-shared words: [0] is
+// set once any role of the CTA gave up, and every other wait of that CTA then returns at once
+// so the CTA drains and exits; [2] (abort_saddr + 8) holds the wait limit in units of 1024
+// cycles.  (A shared-space address costs one register where a generic pointer costs two.)
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, uint32_t abort_saddr,
                                           unsigned int* status, uint32_t code) {
     if (mbar_try_wait(bar, parity)) return true;
@@ -84,14 +100,15 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, uint32_
     for (uint32_t i = 0;; ++i) {
         if (mbar_try_wait(bar, parity)) return true;
         if ((i & 31u) == 31u) {
-            uint32_t gave_up;
+            uint32_t gave_up, limit_k;
             asm volatile("ld.volatile.shared.u32 %0, [%1];" : "=r"(gave_up) : "r"(abort_saddr) : "memory");
             if (gave_up) return false;
-            if (clock64() - t0 > kMaxWaitCycles) break;
+            asm volatile("ld.volatile.shared.u32 %0, [%1+8];" : "=r"(limit_k) : "r"(abort_saddr) : "memory");
+            if (((clock64() - t0) >> 10) > static_cast<long long>(limit_k)) break;
         }
     }
     asm volatile("st.volatile.shared.u32 [%0], %1;" ::"r"(abort_saddr), "r"(1u) : "memory");
-    atomicMax(status, code);
+    report_gave_up(status, code);
     return false;
 }
 

@@ -10,8 +10,18 @@
  * FA_SM100_ERR_* code, never throws, never synchronises the device (except
  * fa_mask_fwd_sm100_device_status, which says so) and never allocates device
  * memory: outputs and the workspace belong to the caller.  Work is enqueued on
- * the caller's stream.  (fa_mask_fwd_sm100 keeps 64 bytes of pinned HOST memory, allocated
- * on first use, for the tile-skip heuristic described at FaMaskFwdPlan.tile_skip.)
+ * the caller's stream.  (fa_mask_fwd_sm100 keeps two small blocks of pinned HOST memory,
+ * allocated on first use: 64 bytes for the tile-skip heuristic described at
+ * FaMaskFwdPlan.tile_skip and, per device, the word through which a kernel reports a wait
+ * that gave up.  The first call on a device and for a kernel variant also sets function
+ * attributes and looks up symbols: make it outside any stream capture.  While a stream is
+ * being captured nothing is allocated; the heuristic and the report are then simply off.)
+ *
+ * Bounded waits: every wait inside the kernels has a limit (about a second).  A wait that
+ * runs out makes its CTA drain and return, leaving `out` partly unwritten, and records a code
+ * in a device status word and in the pinned host word.  Every later fa_mask_fwd_sm100 call on
+ * that device then returns FA_SM100_ERR_DEVICE_WAIT without launching -- found by a plain host
+ * load, no synchronisation -- until fa_mask_fwd_sm100_device_status(device, &st, 1) clears it.
  */
 #ifndef FA_MASK_FWD_SM100_H_
 #define FA_MASK_FWD_SM100_H_
@@ -45,8 +55,13 @@ enum { FA_SM100_FP16 = 0, FA_SM100_BF16 = 1 };
 /* Bits of FaMaskFwdArgs.disable.  Neither changes what is computed, only how. */
 enum {
     FA_SM100_NO_TILE_SKIP = 1,  /* visit every key block even where the mask hides it entirely */
-    FA_SM100_NO_UNIT_CUT = 2    /* every (query pair, head, batch) unit is finished by one CTA, so the
+    FA_SM100_NO_UNIT_CUT = 2,   /* every (query pair, head, batch) unit is finished by one CTA, so the
                                  * result does not depend on the number of SMs */
+    FA_SM100_TEST_STALL_MASK = 0x100  /* tests only: the kernel's mask loads are withheld and its waits
+                                 * get a short limit (FA_SM100_TEST_WAIT_KCYCLES in the environment,
+                                 * units of 1024 SM cycles, default 2000), so that a wait runs out,
+                                 * the kernel returns without writing `out` and the status paths can
+                                 * be exercised without ever hanging a GPU */
 };
 
 #define FA_SM100_MAX_SPLITS 128
@@ -149,8 +164,13 @@ int fa_mask_fwd_sm100(const FaMaskFwdArgs* args, void* workspace, size_t workspa
  * Inputs and outputs are still the caller's.  The Split-KV partials, their LSE and a re-pitched
  * mask go into an array of FA_SM100_STATIC_SCRATCH_BYTES that is part of the library image, so
  * every GPU the library is loaded on holds that much until the process ends.  A call that
- * would need more returns FA_SM100_ERR_WORKSPACE and does nothing; nothing is ever allocated
- * or freed, by this function or by anything it calls.
+ * would need more returns FA_SM100_ERR_WORKSPACE and does nothing (a mask that must be
+ * re-pitched counts in full: 4 x 1000 x 4104 elements, 32.8 MB, is already too much); nothing
+ * is ever allocated or freed, by this function or by anything it calls.  Because the heuristic
+ * that drops the tile-skip pre-pass keeps its state in pinned host memory, which this entry
+ * point may not allocate, the pre-pass (a few microseconds) runs on every eligible call here,
+ * also for masks that have nothing to skip; for the same reason a wait that gave up on the
+ * device is reported to this entry point only once fa_mask_fwd_sm100 has set up the host word.
  *
  * The first call on a device looks up the array's device address (cudaGetSymbolAddress, with
  * that device current) and keeps it; make that first call outside any stream capture.
@@ -158,8 +178,10 @@ int fa_mask_fwd_sm100(const FaMaskFwdArgs* args, void* workspace, size_t workspa
  * There is one array per device and every call uses it from its start: two calls whose GPU
  * work can overlap (different streams, no ordering between them) race on it and corrupt each
  * other's result; calls on one stream are safe.  The array keeps whatever the last call left
- * there; that is harmless because each call writes every scratch word before it reads it --
- * nothing in it has to start at zero. */
+ * there, and nothing in it has to start at zero: partials, LSE values, the re-pitched mask, the
+ * tile-skip flags and the unit counter are written by the call before it reads them, and the
+ * hand-over slots of the unit cutting are guarded by tags that are compared with a value
+ * unique to each launch (stale bytes never equal it) and taken back by their reader. */
 int fa_mask_fwd_sm100_static_scratch(const FaMaskFwdArgs* args, void* stream);
 
 /* Writes an additive mask (0 visible, -inf masked) of shape (batch, 1, seqlen_q, pitch) straight

@@ -312,6 +312,67 @@ def test_cabi_rejects_bad_arguments_on_device():
     assert e.value.code == -6
 
 
+def test_one_mask_plane_for_every_batch_element():
+    """mask_batch_stride = 0: one (1, 1, Sq, Sk) mask serves every batch element (the torch
+    operator wants a contiguous (B, 1, Sq, Sk) mask; a C-ABI caller may pass the stride)."""
+    for (B, H, Hk, Sq, Sk, d, dtype, sk_pad) in [(3, 4, 2, 300, 520, 128, torch.bfloat16, 0),
+                                                 (2, 2, 2, 256, 1027, 64, torch.float16, 0),   # re-pitched
+                                                 (4, 8, 8, 128, 4096, 128, torch.bfloat16, 8)]:  # Split-KV
+        q, k, v, m1 = make_case(B, H, Hk, Sq, Sk, d, dtype, "drop_bias", seed=61, pad_cols=sk_pad)
+        m1 = m1[:1].contiguous()
+        full = m1.expand(B, 1, m1.shape[2], m1.shape[3]).contiguous()
+        q, k, v, m1 = _cuda(q, k, v, m1)
+        out = torch.empty_like(q)
+        args = _cabi.make_args(q=q.data_ptr(), k=k.data_ptr(), v=v.data_ptr(), mask=m1.data_ptr(),
+                               out=out.data_ptr(), batch=B, heads=H, heads_k=Hk, seqlen_q=Sq, seqlen_k=Sk,
+                               head_dim=d, dtype=_cabi.BF16 if dtype == torch.bfloat16 else _cabi.FP16,
+                               mask_seqlen_q=m1.shape[2], mask_seqlen_k=m1.shape[3], mask_batch_stride=0,
+                               mask_row_stride=m1.stride(2))
+        nbytes = _cabi.workspace_bytes(args)
+        ws = torch.empty(max(nbytes, 16), dtype=torch.uint8, device="cuda")
+        for _ in range(3):          # also through the tile-skip pre-pass and its hold-off
+            _cabi.forward(args, ws.data_ptr(), nbytes, torch.cuda.current_stream().cuda_stream)
+        torch.cuda.synchronize()
+        check_against_oracle(out, q, k, v, full, f"broadcast mask {(B, H, Sq, Sk, d)}")
+        # overlapping planes are refused
+        bad = _cabi.make_args(q=q.data_ptr(), k=k.data_ptr(), v=v.data_ptr(), mask=m1.data_ptr(),
+                              out=out.data_ptr(), batch=B, heads=H, heads_k=Hk, seqlen_q=Sq, seqlen_k=Sk,
+                              head_dim=d, dtype=args.dtype, mask_seqlen_q=m1.shape[2],
+                              mask_seqlen_k=m1.shape[3], mask_batch_stride=8, mask_row_stride=m1.stride(2))
+        with pytest.raises(_cabi.FaSm100Error) as e:
+            _cabi.plan(bad)
+        assert e.value.code == -3
+
+
+def test_a_wait_that_runs_out_is_reported_by_the_next_call():
+    """The kernel's mask loads are withheld (a test-only bit) and its waits get a limit of about
+    a millisecond: the softmax threads give up on the mask barrier, every role drains and the
+    kernel returns.  Nothing faults or hangs.  The NEXT forward must refuse to launch with
+    FA_SM100_ERR_DEVICE_WAIT, read from a mapped host word without synchronising; the torch
+    operator turns that into a RuntimeError; clearing the status brings everything back."""
+    from custom_ops_b200 import ops
+    q, k, v, m = _cuda(*make_case(2, 4, 4, 256, 256, 64, torch.bfloat16, "drop10", seed=71))
+    good, _, _ = run_cabi(q, k, v, m)                       # also sets the host word up
+    out = torch.zeros_like(q)
+    kw = dict(q=q.data_ptr(), k=k.data_ptr(), v=v.data_ptr(), mask=m.data_ptr(), out=out.data_ptr(),
+              batch=2, heads=4, heads_k=4, seqlen_q=256, seqlen_k=256, head_dim=64, dtype=_cabi.BF16)
+    stream = torch.cuda.current_stream().cuda_stream
+    _cabi.forward(_cabi.make_args(test_stall_mask=1, **kw), 0, 0, stream)      # launches, gives up on the device
+    torch.cuda.synchronize()
+    with pytest.raises(_cabi.FaSm100Error) as e:
+        _cabi.forward(_cabi.make_args(**kw), 0, 0, stream)
+    assert e.value.code == -10
+    with pytest.raises(RuntimeError):
+        ops.mha_fwd_with_mask(q, k, v, m)
+    # whichever role's clock ran out first reports: the softmax threads' wait for a mask panel
+    # (9) or the MMA thread's wait for P (4); the others see the CTA's abort word and leave
+    assert _cabi.device_status(0, clear=True) in (4, 9)
+    _cabi.forward(_cabi.make_args(**kw), 0, 0, stream)
+    torch.cuda.synchronize()
+    assert torch.equal(out, good)
+    assert torch.equal(ops.mha_fwd_with_mask(q, k, v, m), good)
+
+
 def test_cross_gpu_splitkv_entry_on_one_rank():
     """parallel.splitkv_forward with a one-rank NCCL group: local fp32 partial + LSE,
     gather, merge kernel -- the same calls the multi-GPU path makes."""
@@ -348,11 +409,11 @@ def test_splitkv_single_tile_dual_mode(dtype, case):
 # ---------------------------------------------------------------- units of the last round cut in pieces
 @pytest.mark.parametrize("case", [(2, 16, 16, 1280, 1024, 128, torch.bfloat16),
                                   (3, 12, 4, 1250, 900, 64, torch.float16),
-                                  # three pieces per unit: the first merges two partials
+                                  # three pieces per unit: the last merges two partials
                                   (1, 40, 8, 1024, 3000, 128, torch.float16),
                                   # one unit left over: four pieces, not one per key block
                                   (1, 149, 149, 200, 4000, 64, torch.bfloat16),
-                                  # two pieces per unit, the first one key block longer
+                                  # two pieces per unit, the merging one a key block longer
                                   (1, 111, 37, 512, 1100, 128, torch.bfloat16)])
 def test_units_of_the_last_round_are_cut(case):
     """More single-pass units than SMs: the units of the last, partial round are done in pieces

@@ -45,6 +45,18 @@ def _plan(**kw):
     return _cabi.plan(_cabi.make_args(**base))
 
 
+def test_mask_planes_must_not_overlap():
+    ok = dict(batch=3, heads=2, heads_k=2, seqlen_q=100, seqlen_k=200, mask_seqlen_q=100, mask_seqlen_k=200,
+              mask_row_stride=200)
+    assert _plan(mask_batch_stride=100 * 200, **ok).num_splits >= 1
+    assert _plan(mask_batch_stride=0, **ok).num_splits >= 1             # one plane for every batch element
+    for bad in (8, 200, 100 * 200 - 8):
+        with pytest.raises(_cabi.FaSm100Error) as e:
+            _plan(mask_batch_stride=bad, **ok)
+        assert e.value.code == -3
+    assert _plan(batch=1, heads=2, heads_k=2, seqlen_q=100, seqlen_k=200, mask_batch_stride=8).num_splits >= 1
+
+
 def test_plan_of_the_five_configurations():
     sm = _plan().sm_count                      # 148 where no device can be queried
     p = _plan(batch=4, heads=16, heads_k=16, seqlen_q=2048, seqlen_k=2048)

@@ -47,6 +47,32 @@ def test_static_scratch_matches_workspace_entry_point_twice():
     assert _cabi.device_status(0, clear=True) == 0
 
 
+def test_static_scratch_on_a_dirty_array_unit_cut_and_tile_skip():
+    """Run after the Split-KV case above, so the array holds that call's bytes.  The slots of the
+    unit cutting are guarded by tags that are compared with a value unique to each launch (they
+    are not cleared first), and the tile-skip flags and the unit counter are written by the
+    pre-pass kernel before the attention kernel reads them: neither may be fooled by stale
+    contents.  Each shape runs twice and is compared with the workspace entry point."""
+    stream = torch.cuda.current_stream().cuda_stream
+    # (1, 40, 8, 1024, 3000): 160 units on 148 SMs -> the last round is cut in pieces, scratch < 24 MiB
+    cut = make_case(1, 40, 8, 1024, 3000, 128, torch.float16, "drop_bias", seed=41)
+    # a causal mask over 6 key blocks: the pre-pass finds blocks to skip, units are handed out
+    # from the counter in the scratch array
+    skip = make_case(2, 4, 2, 768, 768, 128, torch.bfloat16, "causal", seed=42)
+    for name, (q, k, v, m) in (("unit cut", cut), ("tile skip", skip)):
+        q, k, v, m = q.cuda(), k.cuda(), v.cuda(), m.cuda()
+        want, _, plan = run_cabi(q, k, v, m)
+        assert 0 < plan.workspace_bytes <= _cabi.STATIC_SCRATCH_BYTES
+        assert (plan.unit_cut >= 2) if name == "unit cut" else (plan.tile_skip == 1)
+        for _ in range(2):
+            got = torch.empty_like(q)
+            _cabi.forward_static_scratch(_args(q, k, v, m, got), stream)
+            torch.cuda.synchronize()
+            assert (got.float() - want.float()).abs().max().item() <= 4e-3, name
+        check_against_oracle(got, q, k, v, m, f"static scratch, {name}")
+    assert _cabi.device_status(0, clear=True) == 0
+
+
 def test_static_scratch_rejects_oversized_requests():
     # 64 heads x 128 rows x 128 splits of fp32 partials is far beyond the built-in array
     q = torch.empty(1, 64, 128, 128, device="cuda", dtype=torch.bfloat16)
