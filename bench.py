@@ -1,7 +1,8 @@
 #!/usr/bin/env python3
 """Benchmark of the masked flash-attention forward (``mha_fwd_with_mask``) on B200.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload standard] [--impl ours|reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload standard]
+                    [--impl ours|reference|reference-cuda] [--scaling weak|strong]
 
 One step = one forward pass of the operator over one batch of the workload
 (default "standard": d128 B4 H16 S2048 bf16, 10 % random -inf mask -- the
@@ -19,12 +20,25 @@ configuration the headline metric is quoted on).  Prints ONE JSON line on rank 0
 * ``cpu_baseline`` the reference's own C++ CPU attention (oracle/_ref, compiled
                from its csrc/fa/cpu sources) on the host cores, on a bounded sample.
 
+* ``all_configs`` (default workload only) the other four benchmark configurations, measured
+               after the headline region with the same method: microseconds, TFLOPS, GB/s, the
+               roofline fraction that binds, and the error against the CPU oracle on one
+               (batch, head) slice.
+
 With ``--gpus N`` (launched under torchrun) every rank runs the workload on its
 own batch shard -- (batch, head) units are independent, there is no collective on
-the data path -- so scaling is weak; the time is the max over ranks.
+the data path -- so scaling is weak; the time is the max over ranks.  The same line
+then also carries ``strong_scaling`` (ONE problem's (batch, kv-head) units spread over
+the ranks, no collective) and ``cross_gpu_splitkv`` (the long-context shape with its keys
+split across the ranks, one NCCL all-gather of the fp32 partials + LSE merge, checked
+against the oracle).  ``--scaling strong`` makes the strong-scaled run the headline.
 
 ``--impl reference`` times the reference's CPU implementation of the same
 workload (rank 0 only) and prints the same line shape with "impl": "reference".
+``--impl reference-cuda`` times the reference's own CUDA extension (its sm8x kernels
+built for sm_100a, loaded from ``baseline/_ref/fa_so``) on the same inputs with the
+same method, in a process that never loads this package's operator; it prints an
+``unavailable`` line where that library is absent.
 """
 from __future__ import annotations
 
@@ -42,7 +56,7 @@ sys.path.insert(0, ROOT)
 
 import torch  # noqa: E402
 
-from custom_ops_b200.workloads import WORKLOADS, make_inputs  # noqa: E402
+from custom_ops_b200.workloads import WORKLOADS, dtype_tag, make_inputs, to_bits  # noqa: E402
 
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 
@@ -50,9 +64,10 @@ FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustain
 # the ncu captures summarised under profiles/ (None until a capture exists).
 LEAD_IN_STEPS = 2      # untimed steps between the barrier and the first timed step (clock ramp)
 
+# (constants from a capture, not measured live: they say which capture they come from)
 NCU_TRAFFIC_BYTES = {
-    "standard": 154.5e6,        # 135.0 MB read + 19.5 MB written (ncu summary of the standard workload)
-    "splitkv_long": 282.1e6,    # 277.45 MB read + 4.61 MB written (ncu summary of the long-context workload)
+    "standard": 154.5e6,        # 135.0 MB read + 19.5 MB written (profiles/fa_mask_fwd_kernel_standard.md)
+    "splitkv_long": 282.1e6,    # 277.45 MB read + 4.61 MB written (profiles/fa_mask_fwd_kernel_splitkv_long.md)
 }
 
 
@@ -207,9 +222,8 @@ def cpu_reference_sample(w, steps: int, warmup: int):
 
     sample = w.with_batch(1)
     q, k, v, m = make_inputs(sample, seed=42)
-    from tests.fa_testlib import bits, tag
-    qb, kb, vb, mb = bits(q), bits(k), bits(v), bits(m)
-    dt = tag(q)
+    qb, kb, vb, mb = to_bits(q), to_bits(k), to_bits(v), to_bits(m)
+    dt = dtype_tag(q)
     cores = os.cpu_count() or 1
     if oracle.load_ref() is not None:
         kind, isa = "reference", oracle.ref_best_isa()
@@ -284,6 +298,258 @@ def run_reference_arm(args, w):
     print(json.dumps(line), flush=True)
 
 
+
+# --------------------------------------------------------------------------- shared measurement
+def oracle_slice_error(out, q_h, k_h, v_h, m_h, b: int, h: int):
+    """max-abs / mean-abs of one (batch, head) slice of ``out`` against the fp32 CPU oracle
+    softmax(QK^T*scale+mask)V (the checker; never on the measured path)."""
+    from oracle import oracle
+
+    g = q_h.shape[1] // k_h.shape[1]
+    qs, ks, vs, ms = q_h[b:b + 1, h:h + 1], k_h[b:b + 1, h // g:h // g + 1], v_h[b:b + 1, h // g:h // g + 1], m_h[b:b + 1]
+    dt = dtype_tag(q_h)
+    args = (to_bits(qs), to_bits(ks), to_bits(vs), to_bits(ms), dt)
+    ref = oracle.port_attn(*args, quantize_p=False) if oracle.load_port() is not None else oracle.attn_fp32(*args)
+    got = out[b:b + 1, h:h + 1].float().cpu().numpy()
+    mx, mean = oracle.errors(got, ref)
+    return float(mx), float(mean)
+
+
+def visited_fraction(w, m_h) -> float:
+    """Share of (256-row query pair, 128-key block) regions that hold a visible key."""
+    mp = -(-w.Sq // 256)
+    nb = -(-w.Sk // 128)
+    fin = ~torch.isneginf(m_h.float())
+    pad = torch.zeros(m_h.shape[0], 1, mp * 256, nb * 128, dtype=torch.bool)
+    pad[:, :, :w.Sq, :w.Sk] = fin[:, :, :w.Sq, :w.Sk]
+    return float(pad.view(m_h.shape[0], mp, 256, nb, 128).any(dim=4).any(dim=2).float().mean())
+
+
+def measure_config(name: str, dev, steps: int, peaks, flush):
+    """One benchmark configuration, kernel-only through the C ABI with the inputs resident in
+    HBM, timed like the headline: L2 evicted before every step (or, for the HBM-bound shape,
+    rotating input copies), CUDA events per step on the launching stream."""
+    from custom_ops_b200 import _cabi
+
+    w = WORKLOADS[name]
+    q_h, k_h, v_h, m_h = make_inputs(w, seed=42)
+    q, k, v, m = (t.to(dev) for t in (q_h, k_h, v_h, m_h))
+    out = torch.empty_like(q)
+    rotate = name == "splitkv_long"
+    sets = [(k, v, m)] + ([(k.clone(), v.clone(), m.clone()) for _ in range(3)] if rotate else [])
+    dt = _cabi.BF16 if w.dtype == torch.bfloat16 else _cabi.FP16
+    cargs = [_cabi.make_args(q=q.data_ptr(), k=ks.data_ptr(), v=vs.data_ptr(), mask=ms.data_ptr(),
+                             out=out.data_ptr(), batch=w.B, heads=w.H, heads_k=w.Hk, seqlen_q=w.Sq,
+                             seqlen_k=w.Sk, head_dim=w.d, dtype=dt, device=dev.index)
+             for ks, vs, ms in sets]
+    plan = _cabi.plan(cargs[0])
+    nbytes = _cabi.workspace_bytes(cargs[0])
+    ws = torch.empty(max(nbytes, 16), dtype=torch.uint8, device=dev)
+    stream = torch.cuda.current_stream(dev)
+    n = [0]
+
+    def step():
+        _cabi.forward(cargs[n[0] % len(cargs)], ws.data_ptr(), nbytes, stream.cuda_stream)
+        n[0] += 1
+
+    for _ in range(5):
+        if not rotate:
+            flush.zero_()
+        step()
+    torch.cuda.synchronize(dev)
+    launches0 = _cabi.launch_count()
+    starts = [torch.cuda.Event(enable_timing=True) for _ in range(steps)]
+    ends = [torch.cuda.Event(enable_timing=True) for _ in range(steps)]
+    for i in range(-LEAD_IN_STEPS, steps):
+        if not rotate:
+            flush.zero_()
+        if i == 0:
+            launches0 = _cabi.launch_count()
+        if i >= 0:
+            starts[i].record(stream)
+        step()
+        if i >= 0:
+            ends[i].record(stream)
+    torch.cuda.synchronize(dev)
+    launches = _cabi.launch_count() - launches0
+    ms = [a.elapsed_time(b) for a, b in zip(starts, ends)]
+    mean_ms = sum(ms) / len(ms)
+    mx, mean = oracle_slice_error(out, q_h, k_h, v_h, m_h, w.B - 1, w.H - 1)
+    visited = visited_fraction(w, m_h) if plan.tile_skip else 1.0
+    tflops = w.flops / (mean_ms * 1e-3) / 1e12
+    gbs = w.bytes / (mean_ms * 1e-3) / 1e9
+    if name == "splitkv_long":
+        bound, achieved, peak, unit = "hbm", gbs, peaks["hbm_gbs"], "GB/s"
+    elif name == "plumbing":
+        bound, achieved, peak, unit = "launch latency", tflops, peaks["bf16_tflops"], "TFLOP/s"
+    else:
+        bound, achieved, peak, unit = "tensor", tflops * visited, peaks["bf16_tflops"], "TFLOP/s"
+    return {"shape": shape_str(w), "us": mean_ms * 1e3, "us_min": min(ms) * 1e3, "us_max": max(ms) * 1e3,
+            "tflops_dense_convention": tflops, "gb_per_s": gbs, "bound": bound, "achieved": achieved,
+            "unit": unit, "peak": peak, "frac": achieved / peak, "visited_block_fraction": visited,
+            "max_abs_vs_oracle": mx, "mean_abs_vs_oracle": mean, "oracle_slice": f"batch {w.B - 1}, head {w.H - 1}",
+            "steps": steps, "kernels_per_step": launches / steps, "num_splits": plan.num_splits,
+            "grid": plan.grid_x, "mask_repitched": bool(plan.mask_repitched),
+            "l2": "4 rotating input copies" if rotate else "256 MB zero-fill before every step"}
+
+
+def measure_strong_scaling(w, dev, steps: int, rank: int, world: int, flush, dist):
+    """ONE problem of workload ``w``: its (batch, kv-head) units are spread over the ranks
+    (custom_ops_b200.parallel.shard_inputs), every rank runs its sub-problems through the C ABI,
+    no collective touches the data path.  Returns (max-over-ranks ms, this rank's slice error)."""
+    from custom_ops_b200 import _cabi, parallel
+
+    q_h, k_h, v_h, m_h = make_inputs(w, seed=42)          # the same problem on every rank
+    pieces_h = parallel.shard_inputs(q_h, k_h, v_h, m_h, world, rank)
+    dt = _cabi.BF16 if w.dtype == torch.bfloat16 else _cabi.FP16
+    stream = torch.cuda.current_stream(dev)
+    jobs = []
+    for qs, ks, vs, ms in pieces_h:
+        qd, kd, vd, md = (t.to(dev) for t in (qs, ks, vs, ms))
+        od = torch.empty_like(qd)
+        a = _cabi.make_args(q=qd.data_ptr(), k=kd.data_ptr(), v=vd.data_ptr(), mask=md.data_ptr(),
+                            out=od.data_ptr(), batch=1, heads=qd.shape[1], heads_k=kd.shape[1],
+                            seqlen_q=w.Sq, seqlen_k=w.Sk, head_dim=w.d, dtype=dt, device=dev.index)
+        nb = _cabi.workspace_bytes(a)
+        jobs.append((a, torch.empty(max(nb, 16), dtype=torch.uint8, device=dev), nb, (qd, kd, vd, md, od)))
+
+    def step():
+        for a, ws, nb, _ in jobs:
+            _cabi.forward(a, ws.data_ptr(), nb, stream.cuda_stream)
+
+    for _ in range(4):
+        flush.zero_()
+        step()
+    torch.cuda.synchronize(dev)
+    dist.barrier()
+    starts = [torch.cuda.Event(enable_timing=True) for _ in range(steps)]
+    ends = [torch.cuda.Event(enable_timing=True) for _ in range(steps)]
+    for i in range(-LEAD_IN_STEPS, steps):
+        flush.zero_()
+        if i >= 0:
+            starts[i].record(stream)
+        step()
+        if i >= 0:
+            ends[i].record(stream)
+    torch.cuda.synchronize(dev)
+    ms = sum(a.elapsed_time(b) for a, b in zip(starts, ends)) / steps
+    err = (0.0, 0.0)
+    if jobs:
+        qs, ks, vs, ms_h = pieces_h[-1]
+        err = oracle_slice_error(jobs[-1][3][4], qs, ks, vs, ms_h, 0, qs.shape[1] - 1)
+    t = torch.tensor([ms, err[0], err[1]], device=dev, dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t[0]), float(t[1]), float(t[2]), len(jobs)
+
+
+def measure_cross_gpu_splitkv(dev, steps: int, rank: int, world: int, dist):
+    """The long-context shape with its keys split across the ranks: local forward into the
+    packed part, one NCCL all-gather, LSE merge; checked against the oracle on one head."""
+    from custom_ops_b200 import parallel
+
+    w = WORKLOADS["splitkv_long"]
+    q_h, k_h, v_h, m_h = make_inputs(w, seed=42)
+    lo, hi = parallel.kv_slice_bounds(w.Sk, world, rank)
+    q = q_h.to(dev)
+    k, v, m = (k_h[:, :, lo:hi].contiguous().to(dev), v_h[:, :, lo:hi].contiguous().to(dev),
+               m_h[:, :, :, lo:hi].contiguous().to(dev))
+    stream = torch.cuda.current_stream(dev)
+    out = None
+    for _ in range(5):
+        out = parallel.splitkv_forward(q, k, v, m)
+    torch.cuda.synchronize(dev)
+    mx, mean = oracle_slice_error(out, q_h, k_h, v_h, m_h, 0, w.H - 1)
+    dist.barrier()
+    starts = [torch.cuda.Event(enable_timing=True) for _ in range(steps)]
+    ends = [torch.cuda.Event(enable_timing=True) for _ in range(steps)]
+    for i in range(-LEAD_IN_STEPS, steps):
+        if i >= 0:
+            starts[i].record(stream)
+        out = parallel.splitkv_forward(q, k, v, m)
+        if i >= 0:
+            ends[i].record(stream)
+    torch.cuda.synchronize(dev)
+    ms = sum(a.elapsed_time(b) for a, b in zip(starts, ends)) / steps
+    # the collective alone, on the same buffers: what the exchange step costs at this size
+    scratch = parallel._SplitKVScratch.get(dev, w.B * w.H * w.Sq, w.d, world)
+    dist.barrier()
+    g0 = torch.cuda.Event(enable_timing=True)
+    g1 = torch.cuda.Event(enable_timing=True)
+    g0.record(stream)
+    for _ in range(steps):
+        dist.all_gather_into_tensor(scratch.gathered, scratch.part)
+    g1.record(stream)
+    torch.cuda.synchronize(dev)
+    gather_ms = g0.elapsed_time(g1) / steps
+    t = torch.tensor([ms, gather_ms, mx, mean], device=dev, dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms, gather_ms, mx, mean = (float(x) for x in t.tolist())
+    return {"shape": shape_str(w), "ranks": world, "keys_per_rank": hi - lo, "us": ms * 1e3,
+            "all_gather_us": gather_ms * 1e3, "part_bytes": scratch.part_floats * 4,
+            "gb_per_s": w.bytes / (ms * 1e-3) / 1e9,
+            "max_abs_vs_oracle": mx, "mean_abs_vs_oracle": mean, "oracle_slice": f"batch 0, head {w.H - 1}",
+            "l2": "inputs stay in place between steps (each rank's key slice is smaller than L2 from 4 ranks on)",
+            "timing": "CUDA events per step on the launching stream, mean over steps, max over ranks"}
+
+
+# --------------------------------------------------------------------------- reference CUDA arm
+def run_reference_cuda_arm(args, w):
+    """The reference's own CUDA extension on this GPU (what a B200 runs today: its sm8x cp.async /
+    mma.sync family built for sm_100a), same inputs, same timing as the reference's own
+    harness (benchmark/benchmark_fa.py:115-132: L2 flush before every iteration, CUDA events).
+    Runs in a process of its own so that its recsys_ops::mha_fwd_with_mask registration never
+    meets this package's."""
+    rank, world, local = dist_env()
+    if rank != 0:
+        return
+    so = os.path.join(ROOT, "baseline", "_ref", "fa_so", "recsys_fa_kernel.so")
+    line = {"impl": "reference-cuda", "metric": METRIC if w.name == "standard" else f"masked attn fwd TFLOPS ({shape_str(w)})"}
+    if not os.path.exists(so) or not torch.cuda.is_available():
+        line["unavailable"] = ("baseline/_ref/fa_so/recsys_fa_kernel.so is not built (the reference's FA group, "
+                               "JIT-built once for sm_100a)" if not os.path.exists(so) else "no CUDA device")
+        print(json.dumps(line), flush=True)
+        return
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    torch.ops.load_library(so)
+    op = torch.ops.recsys_ops.mha_fwd_with_mask
+    names = [w.name] if args.workload != "standard" or args.only_headline else list(WORKLOADS)
+    flush = torch.empty(256 * 1024 * 1024 // 4, dtype=torch.int32, device=dev)
+    results = {}
+    for name in names:
+        wl = WORKLOADS[name]
+        q_h, k_h, v_h, m_h = make_inputs(wl, seed=42)
+        q, k, v, m = (t.to(dev) for t in (q_h, k_h, v_h, m_h))
+        for _ in range(max(3, args.warmup)):
+            out = op(q, k, v, m)
+        torch.cuda.synchronize(dev)
+        ts = []
+        for _ in range(args.steps):
+            flush.zero_()
+            a = torch.cuda.Event(enable_timing=True)
+            b = torch.cuda.Event(enable_timing=True)
+            a.record()
+            out = op(q, k, v, m)
+            b.record()
+            torch.cuda.synchronize(dev)
+            ts.append(a.elapsed_time(b))
+        mean_ms = sum(ts) / len(ts)
+        mx, mean = oracle_slice_error(out, q_h, k_h, v_h, m_h, wl.B - 1, wl.H - 1)
+        results[name] = {"shape": shape_str(wl), "us": mean_ms * 1e3, "us_median": statistics.median(ts) * 1e3,
+                         "tflops_dense_convention": wl.flops / (mean_ms * 1e-3) / 1e12,
+                         "gb_per_s": wl.bytes / (mean_ms * 1e-3) / 1e9,
+                         "max_abs_vs_oracle": mx, "mean_abs_vs_oracle": mean}
+        del q, k, v, m, out
+    head = results[w.name]
+    line.update({"value": head["tflops_dense_convention"], "unit": "TFLOPS", "n_gpus": 1, "steps": args.steps,
+                 "warmup": max(3, args.warmup), "ms_per_step": head["us"] / 1e3, "higher_is_better": True,
+                 "dtype": "bf16" if w.dtype == torch.bfloat16 else "fp16", "data": "synthetic",
+                 "config": {"workload": w.name, "shape": shape_str(w),
+                            "l2": "256 MB zero-fill before every timed step",
+                            "library": "baseline/_ref/fa_so/recsys_fa_kernel.so (reference csrc/fa, -DFA_TARGETS=2, sm_100a)"},
+                 "all_configs": results})
+    print(json.dumps(line), flush=True)
+
 # --------------------------------------------------------------------------- our arm
 METRIC = "masked attn fwd TFLOPS (d128 B4 H16 S2048, 10% random mask)"
 
@@ -315,8 +581,18 @@ def run_ours(args, w):
     # ranks (strong scaling): local forward on the key slice, all-gather of the fp32
     # partials + LSE over NCCL, log-sum-exp merge.
     cross_split = (w.name == "splitkv_long" and world > 1)
-    q_h, k_h, v_h, m_h = make_inputs(w, seed=42 if cross_split else 42 + rank)
-    if cross_split:
+    # --scaling strong: ONE problem, its (batch, kv-head) units spread over the ranks
+    strong = (args.scaling == "strong" and world > 1 and not cross_split)
+    q_h, k_h, v_h, m_h = make_inputs(w, seed=42 if (cross_split or strong) else 42 + rank)
+    if strong:
+        from custom_ops_b200 import parallel
+        pieces = parallel.shard_inputs(q_h, k_h, v_h, m_h, world, rank)
+        if len(pieces) != 1:
+            raise SystemExit("--scaling strong: this rank's units span several batch elements or none; "
+                             "use a rank count that divides the (batch, kv-head) units of one batch element")
+        q_h, k_h, v_h, m_h = pieces[0]
+        w_local = type(w)(w.name, 1, q_h.shape[1], k_h.shape[1], w.Sq, w.Sk, w.d, w.dtype, w.mask_kind, w.sigma)
+    elif cross_split:
         from custom_ops_b200 import parallel
         lo, hi = parallel.kv_slice_bounds(w.Sk, world, rank)
         k_h, v_h, m_h = (k_h[:, :, lo:hi].contiguous(), v_h[:, :, lo:hi].contiguous(),
@@ -324,6 +600,7 @@ def run_ours(args, w):
         w_local = type(w)(w.name, w.B, w.H, w.Hk, w.Sq, hi - lo, w.d, w.dtype, w.mask_kind, w.sigma)
     else:
         w_local = w
+    wl = w_local if strong else w          # the shape this rank launches
     q_h, k_h, v_h, m_h = (t.pin_memory() for t in (q_h, k_h, v_h, m_h))
     q, k, v, m = (t.to(dev, non_blocking=True) for t in (q_h, k_h, v_h, m_h))
     out = torch.empty_like(q)
@@ -338,14 +615,14 @@ def run_ours(args, w):
 
     cargs = _cabi.make_args(
         q=q.data_ptr(), k=k.data_ptr(), v=v.data_ptr(), mask=m.data_ptr(), out=out.data_ptr(),
-        batch=w.B, heads=w.H, heads_k=w.Hk, seqlen_q=w.Sq, seqlen_k=w_local.Sk, head_dim=w.d,
+        batch=wl.B, heads=wl.H, heads_k=wl.Hk, seqlen_q=w.Sq, seqlen_k=w_local.Sk, head_dim=w.d,
         dtype=_cabi.BF16 if w.dtype == torch.bfloat16 else _cabi.FP16, device=local)
     plan = _cabi.plan(cargs)
     cargs_sets = [cargs]
     for ks, vs, ms in sets[1:]:
         cargs_sets.append(_cabi.make_args(
             q=q.data_ptr(), k=ks.data_ptr(), v=vs.data_ptr(), mask=ms.data_ptr(), out=out.data_ptr(),
-            batch=w.B, heads=w.H, heads_k=w.Hk, seqlen_q=w.Sq, seqlen_k=w_local.Sk, head_dim=w.d,
+            batch=wl.B, heads=wl.H, heads_k=wl.Hk, seqlen_q=w.Sq, seqlen_k=w_local.Sk, head_dim=w.d,
             dtype=_cabi.BF16 if w.dtype == torch.bfloat16 else _cabi.FP16, device=local))
     step_no = [0]
     ws_bytes = _cabi.workspace_bytes(cargs)
@@ -441,27 +718,45 @@ def run_ours(args, w):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         mean_ms, med_ms, e2e_ms = (float(x) for x in t.tolist())
 
+    # ---- after the headline regions: the other configurations and the multi-GPU sub-records
+    peaks, peak_src = load_peaks()
+    headline_err = oracle_slice_error(out, q_h, k_h, v_h, m_h, wl.B - 1, wl.H - 1) if not cross_split else None
+    extra = {}
+    sub_steps = max(5, min(args.steps, 10))
+    if w.name == "standard" and not args.only_headline:
+        del sets
+        if world == 1:
+            extra["all_configs"] = {name: measure_config(name, dev, sub_steps, peaks, flush)
+                                    for name in ("plumbing", "gqa_window", "splitkv_long", "ragged_items")}
+        else:
+            if not strong:
+                s_ms, s_mx, s_mean, n_jobs = measure_strong_scaling(w, dev, sub_steps, rank, world, flush, dist)
+                extra["strong_scaling"] = {
+                    "shape": shape_str(w), "ranks": world, "us": s_ms * 1e3,
+                    "tflops": w.flops / (s_ms * 1e-3) / 1e12, "sub_problems_per_rank": n_jobs,
+                    "partition": "(batch, kv-head) units of ONE problem, contiguous range per rank, no collective",
+                    "max_abs_vs_oracle": s_mx, "mean_abs_vs_oracle": s_mean,
+                    "l2": "256 MB zero-fill before every step",
+                    "timing": "CUDA events per step on the launching stream, mean over steps, max over ranks"}
+            extra["cross_gpu_splitkv"] = measure_cross_gpu_splitkv(dev, sub_steps, rank, world, dist)
+        status = _cabi.device_status(local, clear=True)
+        if status != 0:
+            raise SystemExit(f"device status word set ({status}): a kernel gave up on a bounded wait")
+
     if rank == 0:
-        peaks, peak_src = load_peaks()
-        total_flops = w.flops if cross_split else w.flops * world
+        total_flops = w.flops if (cross_split or strong) else w.flops * world
         value = total_flops / (mean_ms * 1e-3) / 1e12
         # Tile skipping: the headline value keeps the dense convention (4*B*H*Sq*Sk*d, mask
         # ignored, like the reference's benchmark); the tensor roofline uses the FLOPs of the
         # key blocks that are actually visited.
-        visited_frac = 1.0
-        if plan.tile_skip:
-            mp = -(-w.Sq // 256)
-            nb = -(-w.Sk // 128)
-            fin = ~torch.isneginf(m_h.float())
-            pad = torch.zeros(w.B, 1, mp * 256, nb * 128, dtype=torch.bool)
-            pad[:, :, :w.Sq, :w.Sk] = fin
-            visited_frac = float(pad.view(w.B, mp, 256, nb, 128).any(dim=4).any(dim=2).float().mean())
+        visited_frac = visited_fraction(wl, m_h) if plan.tile_skip else 1.0
         hbm_bound = w.name == "splitkv_long"
         if hbm_bound:
             achieved = w_local.bytes / (mean_ms * 1e-3) / 1e9
             peak, unit, bound = peaks["hbm_gbs"], "GB/s", "hbm"
         else:
-            achieved = w.flops * visited_frac / (mean_ms * 1e-3) / 1e12
+            # per GPU: a rank's own share of the work over the (max-over-ranks) step time
+            achieved = wl.flops * visited_frac / (mean_ms * 1e-3) / 1e12
             peak, unit, bound = peaks["bf16_tflops"], "TFLOP/s", "tensor"
         in_bytes = sum(t.numel() * t.element_size() for t in (q_h, k_h, v_h, m_h))
         line = {
@@ -469,14 +764,16 @@ def run_ours(args, w):
             "value": value, "unit": "TFLOPS", "n_gpus": world, "steps": args.steps,
             "warmup": max(3, args.warmup), "ms_per_step": mean_ms, "median_ms_per_step": med_ms,
             "min_ms_per_step": min(step_ms), "max_ms_per_step": max(step_ms),
-            "higher_is_better": True, "scaling": "strong" if cross_split else "weak",
+            "higher_is_better": True, "scaling": "strong" if (cross_split or strong) else "weak",
             "vs_baseline": None,
             "dtype": "bf16" if w.dtype == torch.bfloat16 else "fp16", "data": "synthetic",
             "config": {"workload": w.name, "shape": shape_str(w),
                        "parallelism": (f"keys split across {world} ranks, NCCL all-gather of fp32 "
                                        f"partials + LSE merge" if cross_split else
+                                       f"(batch, kv-head) units of one problem spread over {world} rank(s), no collective"
+                                       if strong else
                                        f"(batch, head) sharded, {world} rank(s), no collective"),
-                       "global_batch": w.B if cross_split else w.B * world, "l2": (f"{n_sets} rotating copies of K, V and mask ({n_sets * (w.bytes) / 1e6:.0f} MB in all, L2 is "
+                       "global_batch": w.B if (cross_split or strong) else w.B * world, "l2": (f"{n_sets} rotating copies of K, V and mask ({n_sets * (w.bytes) / 1e6:.0f} MB in all, L2 is "
                               f"126 MB): no input of a step is in L2 when it starts; no flush kernel"
                               if rotate else "256 MB zero-fill before every timed step"),
                        "timing": ("CUDA events per step on the launching stream, mean over steps, max over ranks; "
@@ -501,6 +798,9 @@ def run_ours(args, w):
             "gpu_launches": kernel_launches,
             "clocks": clocks,
         }
+        if headline_err is not None:
+            line["max_abs_vs_oracle"], line["mean_abs_vs_oracle"] = headline_err
+        line.update(extra)
         if world == 1 and not args.no_cpu_baseline:
             try:
                 base = cpu_reference_sample(w, 3, 1)
@@ -521,12 +821,19 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--workload", default="standard", choices=sorted(WORKLOADS))
-    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference", "reference-cuda"])
+    ap.add_argument("--scaling", default="weak", choices=["weak", "strong"],
+                    help="with --gpus N > 1: weak = every rank its own batch shard (default); strong = one "
+                         "problem's (batch, kv-head) units spread over the ranks")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--only-headline", action="store_true",
+                    help="skip the all_configs / strong_scaling / cross_gpu_splitkv sub-records")
     args = ap.parse_args()
     w = WORKLOADS[args.workload]
     if args.impl == "reference":
         run_reference_arm(args, w)
+    elif args.impl == "reference-cuda":
+        run_reference_cuda_arm(args, w)
     else:
         run_ours(args, w)
 

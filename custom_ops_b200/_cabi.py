@@ -30,6 +30,7 @@ EXPORTS = [
     "fa_mask_fwd_sm100_static_scratch",
     "fa_mask_build_sm100",
     "fa_mask_fwd_sm100_combine",
+    "fa_mask_fwd_sm100_combine_packed",
     "fa_mask_fwd_sm100_device_status",
     "fa_mask_fwd_sm100_launch_count",
     "fa_mask_fwd_sm100_strerror",
@@ -123,6 +124,11 @@ def load(path: str | None = None):
         ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int32,
         ctypes.c_int64, ctypes.c_int32, ctypes.c_int32, ctypes.c_int32, ctypes.c_int32,
         ctypes.c_void_p]
+    lib.fa_mask_fwd_sm100_combine_packed.restype = ctypes.c_int
+    lib.fa_mask_fwd_sm100_combine_packed.argtypes = [
+        ctypes.c_void_p, ctypes.c_int64, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int32,
+        ctypes.c_int64, ctypes.c_int32, ctypes.c_int32, ctypes.c_int32, ctypes.c_int32,
+        ctypes.c_void_p]
     lib.fa_mask_build_sm100.restype = ctypes.c_int
     lib.fa_mask_build_sm100.argtypes = [
         ctypes.c_void_p, ctypes.c_int32, ctypes.c_int32, ctypes.c_int32, ctypes.c_int32, ctypes.c_int32,
@@ -210,6 +216,14 @@ def combine(o_parts: int, lse_parts: int, out: int, lse_out: int, num_parts: int
     check(load().fa_mask_fwd_sm100_combine(o_parts or None, lse_parts or None, out or None,
                                            lse_out or None, num_parts, rows, head_dim, dtype,
                                            out_fp32, device, stream or None))
+
+
+def combine_packed(packed: int, part_stride: int, out: int, lse_out: int, num_parts: int, rows: int,
+                   head_dim: int, dtype: int, out_fp32: int, device: int, stream: int):
+    """Merge of parts laid out [O (rows*d) | LSE (rows)] every ``part_stride`` floats."""
+    check(load().fa_mask_fwd_sm100_combine_packed(packed or None, part_stride, out or None,
+                                                  lse_out or None, num_parts, rows, head_dim, dtype,
+                                                  out_fp32, device, stream or None))
 
 
 def build_mask(mask: int, batch: int, seqlen_q: int, seqlen_k: int, pitch: int, dtype: int, causal: int,

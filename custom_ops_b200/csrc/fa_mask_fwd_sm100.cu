@@ -224,6 +224,22 @@ __device__ __forceinline__ void quad_store(const uint32_t (&w)[32], int lane, ch
         if (i - q < rows_left) stg256(row_ptr + (i - q) * row_bytes + q * 32, &w[8 * i]);
 }
 
+// O *= alpha for the 32 rows of the calling warp (each thread its own row and factor).  Rare -
+// a row's reference maximum moves a handful of times per unit - and therefore kept out of line,
+// so that its few hundred instructions do not sit in the softmax loop's instruction stream.
+template <int D>
+__device__ __noinline__ void rescale_rows(uint32_t tO, float alpha) {
+#pragma unroll 1
+    for (int c = 0; c < D / 32; ++c) {
+        uint32_t o[32];
+        tmem_ld32(tO + c * 32, o);
+#pragma unroll
+        for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+        tmem_st32(tO + c * 32, o);
+    }
+    tmem_wait_st();
+}
+
 // Cursor over a ring of mbarrier-guarded buffers: slot index and phase bit, advanced
 // without any division.
 struct Ring {
@@ -843,6 +859,17 @@ fa_mask_fwd_kernel(const __grid_constant__ CUtensorMap tm_q,
                 if (!__all_sync(0xffffffffu, ok)) { alive = false; break; }
                 tc_fence_after();
 
+                if (tail) {
+                    // Last key block of a ragged Sk: columns >= Sk are masked whatever the mask
+                    // tile holds there.  Their scores are overwritten with -inf in tensor memory
+                    // before the row is loaded (s * scale + mask is then -inf for any finite mask
+                    // value), by a loop of single-column stores: a few instructions of code that
+                    // run once per unit, where patching the values in registers took several
+                    // hundred that sat in the middle of this loop's instruction stream.
+#pragma unroll 1
+                    for (int c = p.Sk - col0; c < kBlockN; ++c) tmem_st1(tS + c, 0xff800000u);
+                    tmem_wait_st();
+                }
                 // pass 1: x = s*scale + mask for the whole 128-key block, block maximum
                 uint32_t sreg[kBlockN];
                 tmem_ld128(tS, sreg);
@@ -872,20 +899,6 @@ fa_mask_fwd_kernel(const __grid_constant__ CUtensorMap tm_q,
                     }
                     mbar_arrive(bar_m_empty + 8 * (2 * t + pn));      // panel may be refilled
                 }
-                if (tail) {
-                    // Last key block of a ragged Sk: columns >= Sk are masked whatever the
-                    // mask tile holds there.  Kept out of the main loop on purpose.
-                    mt0 = -INFINITY;
-                    mt1 = -INFINITY;
-#pragma unroll
-                    for (int i = 0; i < kBlockN / 2; ++i) {
-                        const int cc = col0 + 2 * i;
-                        if (cc >= p.Sk) x[i].x = -INFINITY;
-                        if (cc + 1 >= p.Sk) x[i].y = -INFINITY;
-                        mt0 = fmaxf(mt0, x[i].x);
-                        mt1 = fmaxf(mt1, x[i].y);
-                    }
-                }
                 const float mt = fmaxf(mt0, mt1);
 
                 // reference maximum moves only when the row maximum grew by more than 2^8
@@ -902,14 +915,7 @@ fa_mask_fwd_kernel(const __grid_constant__ CUtensorMap tm_q,
                 }
                 if (j > 0 && __any_sync(0xffffffffu, rescale_o)) {
                     // PV of the previous block finished before this block's S was committed.
-#pragma unroll
-                    for (int c = 0; c < D / 32; ++c) {
-                        uint32_t o[32];
-                        tmem_ld32(tO + c * 32, o);
-#pragma unroll
-                        for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
-                        tmem_st32(tO + c * 32, o);
-                    }
+                    rescale_rows<D>(tO, alpha);
                 }
 
                 // pass 2: p = 2^((x - m_ref) * log2 e), fp32 row sum, P rounded to the input dtype
@@ -1220,7 +1226,8 @@ template <int D>
 __global__ void __launch_bounds__(256)
 fa_mask_combine_kernel(const float* __restrict__ o_parts, const float* __restrict__ lse_parts,
                        void* __restrict__ out, float* __restrict__ lse_out, int num_parts,
-                       long long rows, int is_bf16, int out_fp32) {
+                       long long rows, int is_bf16, int out_fp32, long long o_part_stride,
+                       long long lse_part_stride) {
     constexpr int VEC = D / 32;
     const int lane = threadIdx.x & 31;
     const long long row = static_cast<long long>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
@@ -1234,7 +1241,7 @@ fa_mask_combine_kernel(const float* __restrict__ o_parts, const float* __restric
 #pragma unroll
     for (int c = 0; c < FA_SM100_MAX_SPLITS / 32; ++c) {
         const int s = c * 32 + lane;
-        lse_r[c] = (s < num_parts) ? lse_parts[static_cast<long long>(s) * rows + row] : -INFINITY;
+        lse_r[c] = (s < num_parts) ? lse_parts[static_cast<long long>(s) * lse_part_stride + row] : -INFINITY;
         mx = fmaxf(mx, lse_r[c]);
     }
 #pragma unroll
@@ -1267,7 +1274,7 @@ fa_mask_combine_kernel(const float* __restrict__ o_parts, const float* __restric
                 w[u] = __shfl_sync(0xffffffffu, w_r[c], s2 + u);       // same in every lane
                 f[u] = make_float4(0.f, 0.f, 0.f, 0.f);
                 if (part < num_parts && w[u] != 0.f) {
-                    const float* src = o_parts + (static_cast<long long>(part) * rows + row) * D + lane * VEC;
+                    const float* src = o_parts + static_cast<long long>(part) * o_part_stride + row * D + lane * VEC;
                     if constexpr (VEC == 4) {
                         f[u] = __ldg(reinterpret_cast<const float4*>(src));
                     } else {
@@ -1832,8 +1839,12 @@ static int launch_fwd(DeviceInfo* dev, int slot, const CUtensorMap& tq, const CU
 
 static int launch_combine(const float* o_parts, const float* lse_parts, void* out, float* lse_out,
                           int parts, long long rows, int d, int dtype, int out_fp32,
-                          cudaStream_t stream, bool chained = false) {
+                          cudaStream_t stream, bool chained = false, long long o_part_stride = 0,
+                          long long lse_part_stride = 0) {
     if (rows <= 0) return FA_SM100_OK;
+    // distance between consecutive parts, in floats; 0 = the parts follow one another
+    if (o_part_stride == 0) o_part_stride = rows * d;
+    if (lse_part_stride == 0) lse_part_stride = rows;
     const int warps = 8;
     const unsigned blocks = static_cast<unsigned>((rows + warps - 1) / warps);
     if (chained) {
@@ -1853,9 +1864,9 @@ static int launch_combine(const float* o_parts, const float* lse_parts, void* ou
         const int is_bf16 = dtype == FA_SM100_BF16;
         cudaError_t e = (d == 128)
             ? cudaLaunchKernelEx(&cfg, fa_mask_combine_kernel<128>, o_parts, lse_parts, out, lse_out,
-                                 parts, rows, is_bf16, out_fp32)
+                                 parts, rows, is_bf16, out_fp32, o_part_stride, lse_part_stride)
             : cudaLaunchKernelEx(&cfg, fa_mask_combine_kernel<64>, o_parts, lse_parts, out, lse_out,
-                                 parts, rows, is_bf16, out_fp32);
+                                 parts, rows, is_bf16, out_fp32, o_part_stride, lse_part_stride);
         if (e != cudaSuccess) {
             return cuda_failed(__LINE__);
         }
@@ -1864,10 +1875,12 @@ static int launch_combine(const float* o_parts, const float* lse_parts, void* ou
     }
     if (d == 128)
         fa_mask_combine_kernel<128><<<blocks, warps * 32, 0, stream>>>(
-            o_parts, lse_parts, out, lse_out, parts, rows, dtype == FA_SM100_BF16, out_fp32);
+            o_parts, lse_parts, out, lse_out, parts, rows, dtype == FA_SM100_BF16, out_fp32,
+            o_part_stride, lse_part_stride);
     else
         fa_mask_combine_kernel<64><<<blocks, warps * 32, 0, stream>>>(
-            o_parts, lse_parts, out, lse_out, parts, rows, dtype == FA_SM100_BF16, out_fp32);
+            o_parts, lse_parts, out, lse_out, parts, rows, dtype == FA_SM100_BF16, out_fp32,
+            o_part_stride, lse_part_stride);
     if (cudaPeekAtLastError() != cudaSuccess) return cuda_failed(__LINE__);
     ++g_launches;
     return FA_SM100_OK;
@@ -2268,6 +2281,25 @@ int fa_mask_fwd_sm100_combine(const float* o_parts, const float* lse_parts, void
     }
     return fa_sm100::launch_combine(o_parts, lse_parts, out, lse_out, num_parts, rows, head_dim,
                                     dtype, out_fp32, static_cast<cudaStream_t>(stream));
+}
+
+int fa_mask_fwd_sm100_combine_packed(const float* packed, int64_t part_stride, void* out, float* lse_out,
+                                     int32_t num_parts, int64_t rows, int32_t head_dim, int32_t dtype,
+                                     int32_t out_fp32, int32_t device, void* stream) {
+    if (out == nullptr || (num_parts > 0 && packed == nullptr)) return FA_SM100_ERR_NULL;
+    if (head_dim != 64 && head_dim != 128) return FA_SM100_ERR_HEAD_DIM;
+    if (dtype != FA_SM100_FP16 && dtype != FA_SM100_BF16) return FA_SM100_ERR_DTYPE;
+    if (num_parts < 0 || num_parts > FA_SM100_MAX_SPLITS) return FA_SM100_ERR_SPLITS;
+    if (rows < 0 || device < 0 || device >= fa_sm100::kMaxDevices) return FA_SM100_ERR_SHAPE;
+    if (part_stride < rows * (head_dim + 1) || part_stride % 4 != 0) return FA_SM100_ERR_SHAPE;
+    if ((reinterpret_cast<uintptr_t>(packed) & 15u) != 0) return FA_SM100_ERR_ALIGN;
+    fa_sm100::DeviceGuard guard(device);
+    if (guard.err != cudaSuccess) {
+        return fa_sm100::cuda_failed(__LINE__);
+    }
+    return fa_sm100::launch_combine(packed, packed + rows * head_dim, out, lse_out, num_parts, rows, head_dim,
+                                    dtype, out_fp32, static_cast<cudaStream_t>(stream), false, part_stride,
+                                    part_stride);
 }
 
 int fa_mask_fwd_sm100_device_status(int32_t device, uint32_t* status, int32_t clear) {

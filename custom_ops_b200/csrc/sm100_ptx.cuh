@@ -80,7 +80,9 @@ constexpr uint32_t kMaxPolls = 1u << 16;     // cap for the drain loops that hav
 // the host reads at the start of its next call without synchronising anything.
 __device__ unsigned int* g_fa_status_host = nullptr;
 
-__device__ __forceinline__ void report_gave_up(unsigned int* status, uint32_t code) {
+// (kept out of line: it runs at most once per CTA, and inlined into every wait it would sit in
+// the middle of the hot loops' code)
+__device__ __noinline__ void report_gave_up(unsigned int* status, uint32_t code) {
     atomicMax(status, code);
     unsigned int* host_word = *reinterpret_cast<unsigned int* volatile*>(&g_fa_status_host);
     if (host_word != nullptr) {
@@ -311,6 +313,11 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32
           "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]),
           "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
         : "memory");
+}
+
+// one column of the calling warp's 32 lanes
+__device__ __forceinline__ void tmem_st1(uint32_t taddr, uint32_t v) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x1.b32 [%0], {%1};" ::"r"(taddr), "r"(v) : "memory");
 }
 
 __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16]) {

@@ -77,37 +77,78 @@ def kv_slice_bounds(Sk: int, world: int, rank: int) -> Tuple[int, int]:
     return min(b_lo * KV_BLOCK, Sk), min(b_hi * KV_BLOCK, Sk)
 
 
-def _local_partial_cuda(q, k, v, mask):
-    """fp32 normalised output and natural-log LSE of the local key slice (C ABI)."""
+class _SplitKVScratch:
+    """Buffers of the cross-GPU Split-KV, kept between calls per (device, rows, d, world) so the
+    steady state allocates nothing: this rank's packed part ``[O (rows*d) | LSE (rows)]``, the
+    gathered parts of all ranks, and the forward's workspace."""
+
+    _cache: dict = {}
+
+    def __init__(self, device, rows: int, d: int, world: int):
+        # parts are padded to a multiple of 4 floats so that every part starts 16-byte aligned
+        self.part_floats = (rows * (d + 1) + 3) // 4 * 4
+        self.part = torch.empty(self.part_floats, device=device, dtype=torch.float32)
+        self.gathered = torch.empty(world * self.part_floats, device=device, dtype=torch.float32)
+        self.workspace = None
+
+    @classmethod
+    def get(cls, device, rows: int, d: int, world: int) -> "_SplitKVScratch":
+        key = (device.type, device.index, rows, d, world)
+        if key not in cls._cache:
+            if len(cls._cache) >= 8:
+                cls._cache.clear()
+            cls._cache[key] = cls(device, rows, d, world)
+        return cls._cache[key]
+
+    def workspace_for(self, nbytes: int, device):
+        if self.workspace is None or self.workspace.numel() < max(nbytes, 16):
+            self.workspace = torch.empty(max(nbytes, 16), dtype=torch.uint8, device=device)
+        return self.workspace
+
+
+def _check_operands(q, k, v, mask):
+    """The C ABI addresses q, k and v as contiguous (B, H, S, d) tensors; only the mask carries
+    strides.  A sliced view (``k[:, :, lo:hi]``) would silently be read as something else."""
+    for name, t in (("q", q), ("k", k), ("v", v)):
+        if not t.is_contiguous():
+            raise ValueError(f"{name} must be contiguous (call .contiguous() on a sliced view)")
+    for name, t in (("k", k), ("v", v), ("mask", mask)):
+        if t.dtype != q.dtype or t.device != q.device:
+            raise ValueError(f"{name} must have q's dtype and device")
+    if mask.dim() != 4 or mask.stride(3) != 1:
+        raise ValueError("mask must be (B, 1, Sq_m, Sk_m) with unit stride along the keys")
+
+
+def _local_partial_cuda(q, k, v, mask, part: torch.Tensor, scratch: "_SplitKVScratch"):
+    """Normalised fp32 output and natural-log LSE of the local key slice, written straight into
+    ``part`` = [O (rows*d) | LSE (rows)] (C ABI, out_fp32 = 1)."""
     from . import _cabi
 
+    _check_operands(q, k, v, mask)
     B, H, Sq, d = q.shape
-    out = torch.empty((B, H, Sq, d), device=q.device, dtype=torch.float32)
-    lse = torch.empty((B, H, Sq), device=q.device, dtype=torch.float32)
+    rows = B * H * Sq
     args = _cabi.make_args(
-        q=q.data_ptr(), k=k.data_ptr(), v=v.data_ptr(), mask=mask.data_ptr(), out=out.data_ptr(),
-        lse=lse.data_ptr(), batch=B, heads=H, heads_k=k.shape[1], seqlen_q=Sq,
+        q=q.data_ptr(), k=k.data_ptr(), v=v.data_ptr(), mask=mask.data_ptr(), out=part.data_ptr(),
+        lse=part.data_ptr() + 4 * rows * d, batch=B, heads=H, heads_k=k.shape[1], seqlen_q=Sq,
         seqlen_k=k.shape[2], head_dim=d,
         dtype=_cabi.BF16 if q.dtype == torch.bfloat16 else _cabi.FP16,
         mask_seqlen_q=mask.shape[2], mask_seqlen_k=mask.shape[3],
         mask_batch_stride=mask.stride(0), mask_row_stride=mask.stride(2),
         device=q.device.index or 0, out_fp32=1)
     nbytes = _cabi.workspace_bytes(args)
-    ws = torch.empty(max(nbytes, 16), dtype=torch.uint8, device=q.device)
+    ws = scratch.workspace_for(nbytes, q.device)
     _cabi.forward(args, ws.data_ptr(), nbytes, torch.cuda.current_stream(q.device).cuda_stream)
-    return out, lse, ws
 
 
-def _combine_cuda(o_parts, lse_parts, dtype):
-    """(G, rows, d) fp32 partials + (G, rows) LSE -> (rows, d) in ``dtype``."""
+def _combine_cuda(gathered: torch.Tensor, part_floats: int, world: int, rows: int, d: int, dtype):
+    """``world`` packed parts -> (rows, d) in ``dtype``."""
     from . import _cabi
 
-    G, rows, d = o_parts.shape
-    out = torch.empty((rows, d), device=o_parts.device, dtype=dtype)
-    _cabi.combine(o_parts.data_ptr(), lse_parts.data_ptr(), out.data_ptr(), 0, G, rows, d,
-                  _cabi.BF16 if dtype == torch.bfloat16 else _cabi.FP16, 0,
-                  o_parts.device.index or 0,
-                  torch.cuda.current_stream(o_parts.device).cuda_stream)
+    out = torch.empty((rows, d), device=gathered.device, dtype=dtype)
+    _cabi.combine_packed(gathered.data_ptr(), part_floats, out.data_ptr(), 0, world, rows, d,
+                         _cabi.BF16 if dtype == torch.bfloat16 else _cabi.FP16, 0,
+                         gathered.device.index or 0,
+                         torch.cuda.current_stream(gathered.device).cuda_stream)
     return out
 
 
@@ -117,31 +158,37 @@ def splitkv_forward(q, k_local, v_local, mask_local, group=None, *,
     this rank's key slice (see :func:`kv_slice_bounds`), possibly empty.  Every rank
     returns the full result ``(B, H, Sq, d)`` in q's dtype.
 
-    ``local_fn`` / ``combine_fn`` replace the CUDA entry points in host-logic tests
-    that run on CPU ranks; production callers leave them unset.
+    Per call: one forward that writes its fp32 result and LSE straight into this rank's packed
+    part, one ``all_gather_into_tensor`` of the parts (rank-major), one merge kernel that reads
+    the gathered parts where they lie.  Nothing is concatenated, copied or allocated in the
+    steady state (the buffers are kept per shape).
+
+    ``local_fn(q, k, v, mask) -> (O fp32, LSE)`` / ``combine_fn(o_parts, lse_parts, dtype)``
+    replace the CUDA entry points in host-logic tests that run on CPU ranks; production
+    callers leave them unset.
     """
     import torch.distributed as dist
 
     world = dist.get_world_size(group)
     B, H, Sq, d = q.shape
-    local_fn = local_fn or _local_partial_cuda
-    combine_fn = combine_fn or _combine_cuda
-    keep = None
-    if k_local.shape[2] > 0:
-        res = local_fn(q, k_local, v_local, mask_local)
-        o_loc, lse_loc = res[0], res[1]
-        keep = res[2:] if len(res) > 2 else None      # scratch stays alive until the stream is done
-    else:
-        o_loc = torch.zeros((B, H, Sq, d), device=q.device, dtype=torch.float32)
-        lse_loc = torch.full((B, H, Sq), float("-inf"), device=q.device, dtype=torch.float32)
     rows = B * H * Sq
-    # one packed buffer per rank: [O (rows*d) | LSE (rows)] -> a single all_gather
-    packed = torch.cat([o_loc.reshape(-1), lse_loc.reshape(-1)])
-    flat = torch.empty(world * packed.numel(), device=q.device, dtype=torch.float32)
-    dist.all_gather_into_tensor(flat, packed, group=group)      # rank-major
-    gathered = flat.view(world, packed.numel())
-    o_parts = gathered[:, :rows * d].reshape(world, rows, d).contiguous()
-    lse_parts = gathered[:, rows * d:].reshape(world, rows).contiguous()
-    out = combine_fn(o_parts, lse_parts, q.dtype)
-    del keep
+    scratch = _SplitKVScratch.get(q.device, rows, d, world)
+    part, pf = scratch.part, scratch.part_floats
+    if k_local.shape[2] > 0:
+        if local_fn is None:
+            _local_partial_cuda(q, k_local, v_local, mask_local, part, scratch)
+        else:
+            o_loc, lse_loc = local_fn(q, k_local, v_local, mask_local)[:2]
+            part[:rows * d].copy_(o_loc.reshape(-1))
+            part[rows * d:rows * (d + 1)].copy_(lse_loc.reshape(-1))
+    else:
+        part[:rows * d].zero_()
+        part[rows * d:rows * (d + 1)].fill_(float("-inf"))
+    dist.all_gather_into_tensor(scratch.gathered, part, group=group)      # rank-major
+    if combine_fn is None:
+        out = _combine_cuda(scratch.gathered, pf, world, rows, d, q.dtype)
+    else:
+        g = scratch.gathered.view(world, pf)
+        out = combine_fn(g[:, :rows * d].reshape(world, rows, d).contiguous(),
+                         g[:, rows * d:rows * (d + 1)].contiguous(), q.dtype)
     return out.reshape(B, H, Sq, d)

@@ -16,6 +16,7 @@ from __future__ import annotations
 import dataclasses
 import math
 
+import numpy as np
 import torch
 
 
@@ -105,3 +106,13 @@ def small_analogue(w: Workload, Sq: int, Sk: int, B: int = 1, H: int | None = No
     H = H or w.H
     Hk = max(1, H // (w.H // w.Hk))
     return dataclasses.replace(w, name=w.name + "_small", B=B, H=H, Hk=Hk, Sq=Sq, Sk=Sk)
+
+
+def to_bits(t: torch.Tensor) -> np.ndarray:
+    """The raw 16-bit patterns of a float16 / bfloat16 tensor as a numpy uint16 array (numpy has
+    no bfloat16; checkers that work on bit patterns take this)."""
+    return t.detach().cpu().contiguous().view(torch.int16).numpy().view(np.uint16)
+
+
+def dtype_tag(t: torch.Tensor) -> str:
+    return "bf16" if t.dtype == torch.bfloat16 else "fp16"

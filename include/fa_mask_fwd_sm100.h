@@ -211,6 +211,17 @@ int fa_mask_fwd_sm100_combine(const float* o_parts, const float* lse_parts, void
                               float* lse_out, int32_t num_parts, int64_t rows, int32_t head_dim,
                               int32_t dtype, int32_t out_fp32, int32_t device, void* stream);
 
+/* The same merge for parts that arrive packed, as one all-gather over the ranks of a cross-GPU
+ * Split-KV delivers them: part s occupies `part_stride` floats starting at packed + s *
+ * part_stride, first its (rows, head_dim) fp32 output, directly behind it its (rows) LSE values
+ * (so part_stride >= rows * (head_dim + 1); a multiple of 4 keeps every part 16-byte aligned).
+ * A rank writes its own part with FaMaskFwdArgs.out = part, .lse = part + rows * head_dim,
+ * .out_fp32 = 1, and nothing has to be copied or re-packed between the forward, the
+ * collective and the merge.  No counterpart in the reference, which has no distributed code. */
+int fa_mask_fwd_sm100_combine_packed(const float* packed, int64_t part_stride, void* out, float* lse_out,
+                                     int32_t num_parts, int64_t rows, int32_t head_dim, int32_t dtype,
+                                     int32_t out_fp32, int32_t device, void* stream);
+
 /* Synchronises `device` and returns in *status the sticky device-side status
  * word: 0, or the code of the first bounded wait that ran out.  Clears it when
  * `clear` != 0.  No counterpart in the reference, whose kernels wait unbounded. */

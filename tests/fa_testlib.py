@@ -10,12 +10,7 @@ from custom_ops_b200 import _cabi
 from oracle import oracle
 
 
-def bits(t: torch.Tensor) -> np.ndarray:
-    return t.detach().cpu().contiguous().view(torch.int16).numpy().view(np.uint16)
-
-
-def tag(t: torch.Tensor) -> str:
-    return "bf16" if t.dtype == torch.bfloat16 else "fp16"
+from custom_ops_b200.workloads import dtype_tag as tag, to_bits as bits  # noqa: E402,F401
 
 
 def from_bits(b: np.ndarray, dtype: str) -> torch.Tensor:

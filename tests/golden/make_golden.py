@@ -88,7 +88,11 @@ def make_case(gen, dtype, B, H, Hk, Sq, Sk, d, kind, pad_rows, pad_cols):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default=os.environ.get("CUSTOM_OPS_REFERENCE", "/root/reference"))
+    here = os.path.dirname(os.path.abspath(__file__))
+    beside = os.path.join(os.path.dirname(os.path.dirname(os.path.dirname(here))), "reference")
+    ap.add_argument("--reference", default=os.environ.get("CUSTOM_OPS_REFERENCE", beside),
+                    help="checkout of the reference (default: $CUSTOM_OPS_REFERENCE, else a directory "
+                         "'reference' beside this repository)")
     ap.add_argument("--out", default=os.path.join(os.path.dirname(os.path.abspath(__file__)),
                                                   "ref_attn_cases.npz"))
     args = ap.parse_args()
