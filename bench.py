@@ -408,7 +408,7 @@ def measure_strong_scaling(w, dev, steps: int, rank: int, world: int, flush, dis
         qd, kd, vd, md = (t.to(dev) for t in (qs, ks, vs, ms))
         od = torch.empty_like(qd)
         a = _cabi.make_args(q=qd.data_ptr(), k=kd.data_ptr(), v=vd.data_ptr(), mask=md.data_ptr(),
-                            out=od.data_ptr(), batch=1, heads=qd.shape[1], heads_k=kd.shape[1],
+                            out=od.data_ptr(), batch=qd.shape[0], heads=qd.shape[1], heads_k=kd.shape[1],
                             seqlen_q=w.Sq, seqlen_k=w.Sk, head_dim=w.d, dtype=dt, device=dev.index)
         nb = _cabi.workspace_bytes(a)
         jobs.append((a, torch.empty(max(nb, 16), dtype=torch.uint8, device=dev), nb, (qd, kd, vd, md, od)))
@@ -436,7 +436,7 @@ def measure_strong_scaling(w, dev, steps: int, rank: int, world: int, flush, dis
     err = (0.0, 0.0)
     if jobs:
         qs, ks, vs, ms_h = pieces_h[-1]
-        err = oracle_slice_error(jobs[-1][3][4], qs, ks, vs, ms_h, 0, qs.shape[1] - 1)
+        err = oracle_slice_error(jobs[-1][3][4], qs, ks, vs, ms_h, qs.shape[0] - 1, qs.shape[1] - 1)
     t = torch.tensor([ms, err[0], err[1]], device=dev, dtype=torch.float64)
     dist.all_reduce(t, op=dist.ReduceOp.MAX)
     return float(t[0]), float(t[1]), float(t[2]), len(jobs)
@@ -444,7 +444,9 @@ def measure_strong_scaling(w, dev, steps: int, rank: int, world: int, flush, dis
 
 def measure_cross_gpu_splitkv(dev, steps: int, rank: int, world: int, dist):
     """The long-context shape with its keys split across the ranks: local forward into the
-    packed part, one NCCL all-gather, LSE merge; checked against the oracle on one head."""
+    packed part, exchange, LSE merge; checked against the oracle on one head.  Both exchanges
+    are timed: through peer-addressable memory inside the merge kernel, and one NCCL
+    all-gather followed by the merge."""
     from custom_ops_b200 import parallel
 
     w = WORKLOADS["splitkv_long"]
@@ -454,23 +456,30 @@ def measure_cross_gpu_splitkv(dev, steps: int, rank: int, world: int, dist):
     k, v, m = (k_h[:, :, lo:hi].contiguous().to(dev), v_h[:, :, lo:hi].contiguous().to(dev),
                m_h[:, :, :, lo:hi].contiguous().to(dev))
     stream = torch.cuda.current_stream(dev)
-    out = None
-    for _ in range(5):
-        out = parallel.splitkv_forward(q, k, v, m)
-    torch.cuda.synchronize(dev)
-    mx, mean = oracle_slice_error(out, q_h, k_h, v_h, m_h, 0, w.H - 1)
-    dist.barrier()
-    starts = [torch.cuda.Event(enable_timing=True) for _ in range(steps)]
-    ends = [torch.cuda.Event(enable_timing=True) for _ in range(steps)]
-    for i in range(-LEAD_IN_STEPS, steps):
-        if i >= 0:
-            starts[i].record(stream)
-        out = parallel.splitkv_forward(q, k, v, m)
-        if i >= 0:
-            ends[i].record(stream)
-    torch.cuda.synchronize(dev)
-    ms = sum(a.elapsed_time(b) for a, b in zip(starts, ends)) / steps
-    # the collective alone, on the same buffers: what the exchange step costs at this size
+
+    def timed(exchange):
+        out = None
+        for _ in range(5):
+            out = parallel.splitkv_forward(q, k, v, m, exchange=exchange)
+        torch.cuda.synchronize(dev)
+        mx, mean = oracle_slice_error(out, q_h, k_h, v_h, m_h, 0, w.H - 1)
+        dist.barrier()
+        starts = [torch.cuda.Event(enable_timing=True) for _ in range(steps)]
+        ends = [torch.cuda.Event(enable_timing=True) for _ in range(steps)]
+        for i in range(-LEAD_IN_STEPS, steps):
+            if i >= 0:
+                starts[i].record(stream)
+            out = parallel.splitkv_forward(q, k, v, m, exchange=exchange)
+            if i >= 0:
+                ends[i].record(stream)
+        torch.cuda.synchronize(dev)
+        ms = sum(a.elapsed_time(b) for a, b in zip(starts, ends)) / steps
+        t = torch.tensor([ms, mx, mean], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return [float(x) for x in t.tolist()]
+
+    nccl_ms, nccl_mx, nccl_mean = timed("nccl")
+    # the collective alone, on the same buffers: what that exchange step costs at this size
     scratch = parallel._SplitKVScratch.get(dev, w.B * w.H * w.Sq, w.d, world)
     dist.barrier()
     g0 = torch.cuda.Event(enable_timing=True)
@@ -480,14 +489,29 @@ def measure_cross_gpu_splitkv(dev, steps: int, rank: int, world: int, dist):
         dist.all_gather_into_tensor(scratch.gathered, scratch.part)
     g1.record(stream)
     torch.cuda.synchronize(dev)
-    gather_ms = g0.elapsed_time(g1) / steps
-    t = torch.tensor([ms, gather_ms, mx, mean], device=dev, dtype=torch.float64)
+    t = torch.tensor([g0.elapsed_time(g1) / steps], device=dev, dtype=torch.float64)
     dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms, gather_ms, mx, mean = (float(x) for x in t.tolist())
-    return {"shape": shape_str(w), "ranks": world, "keys_per_rank": hi - lo, "us": ms * 1e3,
-            "all_gather_us": gather_ms * 1e3, "part_bytes": scratch.part_floats * 4,
-            "gb_per_s": w.bytes / (ms * 1e-3) / 1e9,
-            "max_abs_vs_oracle": mx, "mean_abs_vs_oracle": mean, "oracle_slice": f"batch 0, head {w.H - 1}",
+    gather_ms = float(t[0])
+    # every rank must take the same branch: agree on whether the peer exchange can be set up
+    can = torch.tensor([1 if parallel.peer_exchange_available() else 0], device=dev)
+    dist.all_reduce(can, op=dist.ReduceOp.MIN)
+    peer = None
+    peer_note = "symmetric memory not available in this torch build"
+    if int(can[0]):
+        try:
+            peer = timed("peer")
+            peer_note = "parts in symmetric memory, read over NVLink by the merge kernel (plain loads, bounded wait)"
+        except Exception as e:  # noqa: BLE001
+            peer_note = f"peer exchange failed to set up: {str(e)[:160]}"
+    best_ms, mx, mean = (peer if peer is not None and peer[0] <= nccl_ms else (nccl_ms, nccl_mx, nccl_mean))
+    return {"shape": shape_str(w), "ranks": world, "keys_per_rank": hi - lo, "us": best_ms * 1e3,
+            "exchange": "peer" if (peer is not None and peer[0] <= nccl_ms) else "nccl",
+            "us_peer_exchange": None if peer is None else peer[0] * 1e3,
+            "us_nccl_exchange": nccl_ms * 1e3, "nccl_all_gather_alone_us": gather_ms * 1e3,
+            "peer_exchange": peer_note, "part_bytes": scratch.part_floats * 4,
+            "gb_per_s": w.bytes / (best_ms * 1e-3) / 1e9,
+            "max_abs_vs_oracle": max(mx, nccl_mx), "mean_abs_vs_oracle": max(mean, nccl_mean),
+            "oracle_slice": f"batch 0, head {w.H - 1}",
             "l2": "inputs stay in place between steps (each rank's key slice is smaller than L2 from 4 ranks on)",
             "timing": "CUDA events per step on the launching stream, mean over steps, max over ranks"}
 

@@ -31,6 +31,7 @@ EXPORTS = [
     "fa_mask_build_sm100",
     "fa_mask_fwd_sm100_combine",
     "fa_mask_fwd_sm100_combine_packed",
+    "fa_mask_fwd_sm100_combine_peers",
     "fa_mask_fwd_sm100_device_status",
     "fa_mask_fwd_sm100_launch_count",
     "fa_mask_fwd_sm100_strerror",
@@ -129,6 +130,11 @@ def load(path: str | None = None):
         ctypes.c_void_p, ctypes.c_int64, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int32,
         ctypes.c_int64, ctypes.c_int32, ctypes.c_int32, ctypes.c_int32, ctypes.c_int32,
         ctypes.c_void_p]
+    lib.fa_mask_fwd_sm100_combine_peers.restype = ctypes.c_int
+    lib.fa_mask_fwd_sm100_combine_peers.argtypes = [
+        ctypes.c_void_p, ctypes.c_int64, ctypes.c_int64, ctypes.c_int32, ctypes.c_int32, ctypes.c_uint32,
+        ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int64, ctypes.c_int32, ctypes.c_int32, ctypes.c_int32,
+        ctypes.c_int32, ctypes.c_void_p]
     lib.fa_mask_build_sm100.restype = ctypes.c_int
     lib.fa_mask_build_sm100.argtypes = [
         ctypes.c_void_p, ctypes.c_int32, ctypes.c_int32, ctypes.c_int32, ctypes.c_int32, ctypes.c_int32,
@@ -224,6 +230,15 @@ def combine_packed(packed: int, part_stride: int, out: int, lse_out: int, num_pa
     check(load().fa_mask_fwd_sm100_combine_packed(packed or None, part_stride, out or None,
                                                   lse_out or None, num_parts, rows, head_dim, dtype,
                                                   out_fp32, device, stream or None))
+
+
+def combine_peers(part_table: int, part_offset: int, flag_offset: int, rank: int, world: int, seq: int,
+                  out: int, lse_out: int, rows: int, head_dim: int, dtype: int, out_fp32: int, device: int,
+                  stream: int):
+    """Merge with the exchange through peer-addressable memory built in (see the header)."""
+    check(load().fa_mask_fwd_sm100_combine_peers(part_table or None, part_offset, flag_offset, rank, world,
+                                                 seq, out or None, lse_out or None, rows, head_dim, dtype,
+                                                 out_fp32, device, stream or None))
 
 
 def build_mask(mask: int, batch: int, seqlen_q: int, seqlen_k: int, pitch: int, dtype: int, causal: int,

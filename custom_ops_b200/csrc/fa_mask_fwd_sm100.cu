@@ -94,7 +94,8 @@ constexpr uint32_t kPanelBytes = 128 * 64 * 2;            // 128 rows x 64 colum
 // Status codes written to the device status word when a bounded wait runs out.
 enum : uint32_t {
     kStTmaEmpty = 1, kStMmaQ = 2, kStMmaKv = 3, kStMmaP = 4, kStSoftmaxS = 5, kStSoftmaxO = 6,
-    kStDrain = 7, kStMaskEmpty = 8, kStSoftmaxMask = 9, kStList = 10, kStPartial = 11
+    kStDrain = 7, kStMaskEmpty = 8, kStSoftmaxMask = 9, kStList = 10, kStPartial = 11,
+    kStPeer = 12     // the merge of a cross-GPU Split-KV waited in vain for another rank's part
 };
 
 __device__ unsigned int g_fa_status = 0;
@@ -1222,18 +1223,74 @@ fa_mask_fwd_kernel(const __grid_constant__ CUtensorMap tm_q,
 // Split-KV merge: one warp per output row.
 //   out = sum_s w_s o_s / sum_s w_s,  w_s = exp(lse_s - max_s lse_s)
 // ---------------------------------------------------------------------------------
+// Exchange of the parts of a cross-GPU Split-KV through peer memory.  Every rank keeps its
+// part in a buffer that all ranks of the box can address (symmetric memory: the same layout on
+// every rank, `parts[r]` = base of rank r's buffer as seen from this GPU).  The merge kernel of
+// rank r first tells every rank "my part of call `seq` is complete" with one store into that
+// rank's flag words, then waits - bounded - until its own flag words show `seq` from every
+// rank, and then reads the other ranks' parts straight over NVLink with plain loads: no
+// collective library call, no copy into local memory first.
+struct PeerExchange {
+    const float* const* parts;   // device array [world]; NULL: the parts are local (no exchange)
+    long long part_offset;       // floats from a buffer's base to the part of this call
+    long long flag_offset;       // floats from a buffer's base to its `world` flag words
+    int rank, world;
+    unsigned int seq;            // sequence number of this call, the same on every rank, never 0
+    unsigned int wait_kcycles;   // limit of the wait, in units of 1024 SM cycles
+    unsigned int* status;
+};
+
+__device__ __forceinline__ unsigned int ld_acquire_sys_u32(const unsigned int* p) {
+    unsigned int v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+
+__device__ __forceinline__ void st_release_sys_u32(unsigned int* p, unsigned int v) {
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+
 template <int D>
 __global__ void __launch_bounds__(256)
 fa_mask_combine_kernel(const float* __restrict__ o_parts, const float* __restrict__ lse_parts,
                        void* __restrict__ out, float* __restrict__ lse_out, int num_parts,
                        long long rows, int is_bf16, int out_fp32, long long o_part_stride,
-                       long long lse_part_stride) {
+                       long long lse_part_stride, const PeerExchange px) {
     constexpr int VEC = D / 32;
     const int lane = threadIdx.x & 31;
     const long long row = static_cast<long long>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
     // When chained behind the attention kernel with programmatic dependent launch, the
     // partials are only valid after this returns; otherwise it returns at once.
     pdl_wait_prior_grid();
+    const bool peers = px.parts != nullptr;
+    if (peers) {
+        __shared__ int s_ok;
+        if (blockIdx.x == 0 && static_cast<int>(threadIdx.x) < px.world) {
+            // this rank's part was written by the kernels before this one in the stream
+            __threadfence_system();
+            unsigned int* f = reinterpret_cast<unsigned int*>(
+                                  const_cast<float*>(px.parts[threadIdx.x]) + px.flag_offset) + px.rank;
+            st_release_sys_u32(f, px.seq);
+        }
+        if (threadIdx.x == 0) {
+            const unsigned int* mine = reinterpret_cast<const unsigned int*>(px.parts[px.rank] + px.flag_offset);
+            const long long t0 = clock64();
+            int ok = 1;
+            for (int r = 0; r < px.world && ok; ++r) {
+                // (a rank that is already one call ahead shows a larger number: that is fine too)
+                while (static_cast<int>(ld_acquire_sys_u32(mine + r) - px.seq) < 0) {
+                    if (((clock64() - t0) >> 10) > static_cast<long long>(px.wait_kcycles)) {
+                        ok = 0;
+                        break;
+                    }
+                }
+            }
+            if (!ok) report_gave_up(px.status, kStPeer);
+            s_ok = ok;
+        }
+        __syncthreads();
+        if (!s_ok) return;
+    }
     if (row >= rows) return;
 
     float lse_r[FA_SM100_MAX_SPLITS / 32];
@@ -1241,7 +1298,10 @@ fa_mask_combine_kernel(const float* __restrict__ o_parts, const float* __restric
 #pragma unroll
     for (int c = 0; c < FA_SM100_MAX_SPLITS / 32; ++c) {
         const int s = c * 32 + lane;
-        lse_r[c] = (s < num_parts) ? lse_parts[static_cast<long long>(s) * lse_part_stride + row] : -INFINITY;
+        lse_r[c] = -INFINITY;
+        if (s < num_parts)
+            lse_r[c] = peers ? ld_cg_f32(px.parts[s] + px.part_offset + rows * D + row)
+                             : lse_parts[static_cast<long long>(s) * lse_part_stride + row];
         mx = fmaxf(mx, lse_r[c]);
     }
 #pragma unroll
@@ -1274,12 +1334,27 @@ fa_mask_combine_kernel(const float* __restrict__ o_parts, const float* __restric
                 w[u] = __shfl_sync(0xffffffffu, w_r[c], s2 + u);       // same in every lane
                 f[u] = make_float4(0.f, 0.f, 0.f, 0.f);
                 if (part < num_parts && w[u] != 0.f) {
-                    const float* src = o_parts + static_cast<long long>(part) * o_part_stride + row * D + lane * VEC;
+                    // (another GPU's memory is read past the L1: the same addresses carry new
+                    // data every other call)
+                    const float* src = (peers ? px.parts[part] + px.part_offset
+                                              : o_parts + static_cast<long long>(part) * o_part_stride) +
+                                       row * D + lane * VEC;
                     if constexpr (VEC == 4) {
-                        f[u] = __ldg(reinterpret_cast<const float4*>(src));
+                        if (peers) {
+                            const uint4 g = ld_cg_v4(src);
+                            f[u] = make_float4(__uint_as_float(g.x), __uint_as_float(g.y), __uint_as_float(g.z),
+                                               __uint_as_float(g.w));
+                        } else {
+                            f[u] = __ldg(reinterpret_cast<const float4*>(src));
+                        }
                     } else {
-                        const float2 g = __ldg(reinterpret_cast<const float2*>(src));
-                        f[u].x = g.x; f[u].y = g.y;
+                        if (peers) {
+                            f[u].x = ld_cg_f32(src);
+                            f[u].y = ld_cg_f32(src + 1);
+                        } else {
+                            const float2 g = __ldg(reinterpret_cast<const float2*>(src));
+                            f[u].x = g.x; f[u].y = g.y;
+                        }
                     }
                 } else {
                     w[u] = 0.f;
@@ -1840,8 +1915,11 @@ static int launch_fwd(DeviceInfo* dev, int slot, const CUtensorMap& tq, const CU
 static int launch_combine(const float* o_parts, const float* lse_parts, void* out, float* lse_out,
                           int parts, long long rows, int d, int dtype, int out_fp32,
                           cudaStream_t stream, bool chained = false, long long o_part_stride = 0,
-                          long long lse_part_stride = 0) {
+                          long long lse_part_stride = 0, const PeerExchange* peer = nullptr) {
     if (rows <= 0) return FA_SM100_OK;
+    PeerExchange px;
+    std::memset(&px, 0, sizeof(px));
+    if (peer != nullptr) px = *peer;
     // distance between consecutive parts, in floats; 0 = the parts follow one another
     if (o_part_stride == 0) o_part_stride = rows * d;
     if (lse_part_stride == 0) lse_part_stride = rows;
@@ -1864,9 +1942,9 @@ static int launch_combine(const float* o_parts, const float* lse_parts, void* ou
         const int is_bf16 = dtype == FA_SM100_BF16;
         cudaError_t e = (d == 128)
             ? cudaLaunchKernelEx(&cfg, fa_mask_combine_kernel<128>, o_parts, lse_parts, out, lse_out,
-                                 parts, rows, is_bf16, out_fp32, o_part_stride, lse_part_stride)
+                                 parts, rows, is_bf16, out_fp32, o_part_stride, lse_part_stride, px)
             : cudaLaunchKernelEx(&cfg, fa_mask_combine_kernel<64>, o_parts, lse_parts, out, lse_out,
-                                 parts, rows, is_bf16, out_fp32, o_part_stride, lse_part_stride);
+                                 parts, rows, is_bf16, out_fp32, o_part_stride, lse_part_stride, px);
         if (e != cudaSuccess) {
             return cuda_failed(__LINE__);
         }
@@ -1876,11 +1954,11 @@ static int launch_combine(const float* o_parts, const float* lse_parts, void* ou
     if (d == 128)
         fa_mask_combine_kernel<128><<<blocks, warps * 32, 0, stream>>>(
             o_parts, lse_parts, out, lse_out, parts, rows, dtype == FA_SM100_BF16, out_fp32,
-            o_part_stride, lse_part_stride);
+            o_part_stride, lse_part_stride, px);
     else
         fa_mask_combine_kernel<64><<<blocks, warps * 32, 0, stream>>>(
             o_parts, lse_parts, out, lse_out, parts, rows, dtype == FA_SM100_BF16, out_fp32,
-            o_part_stride, lse_part_stride);
+            o_part_stride, lse_part_stride, px);
     if (cudaPeekAtLastError() != cudaSuccess) return cuda_failed(__LINE__);
     ++g_launches;
     return FA_SM100_OK;
@@ -2300,6 +2378,41 @@ int fa_mask_fwd_sm100_combine_packed(const float* packed, int64_t part_stride, v
     return fa_sm100::launch_combine(packed, packed + rows * head_dim, out, lse_out, num_parts, rows, head_dim,
                                     dtype, out_fp32, static_cast<cudaStream_t>(stream), false, part_stride,
                                     part_stride);
+}
+
+int fa_mask_fwd_sm100_combine_peers(const void* part_table, int64_t part_offset, int64_t flag_offset,
+                                    int32_t rank, int32_t world, uint32_t seq, void* out, float* lse_out,
+                                    int64_t rows, int32_t head_dim, int32_t dtype, int32_t out_fp32,
+                                    int32_t device, void* stream) {
+    if (out == nullptr || part_table == nullptr) return FA_SM100_ERR_NULL;
+    if (head_dim != 64 && head_dim != 128) return FA_SM100_ERR_HEAD_DIM;
+    if (dtype != FA_SM100_FP16 && dtype != FA_SM100_BF16) return FA_SM100_ERR_DTYPE;
+    if (world < 1 || world > FA_SM100_MAX_SPLITS || rank < 0 || rank >= world) return FA_SM100_ERR_SPLITS;
+    if (rows < 0 || seq == 0 || part_offset < 0 || part_offset % 4 != 0 || flag_offset < 0 ||
+        device < 0 || device >= fa_sm100::kMaxDevices)
+        return FA_SM100_ERR_SHAPE;
+    fa_sm100::DeviceGuard guard(device);
+    if (guard.err != cudaSuccess) {
+        return fa_sm100::cuda_failed(__LINE__);
+    }
+    fa_sm100::DeviceInfo* dev = nullptr;
+    fa_sm100::query_device(device, &dev);
+    int rc = fa_sm100::status_pointer(dev);
+    if (rc != FA_SM100_OK) return rc;
+    fa_sm100::status_host_setup(dev, static_cast<cudaStream_t>(stream), true);
+    if (dev->status_host != nullptr && *static_cast<volatile unsigned int*>(dev->status_host) != 0u)
+        return FA_SM100_ERR_DEVICE_WAIT;
+    fa_sm100::PeerExchange px;
+    px.parts = static_cast<const float* const*>(part_table);
+    px.part_offset = part_offset;
+    px.flag_offset = flag_offset;
+    px.rank = rank;
+    px.world = world;
+    px.seq = seq;
+    px.wait_kcycles = fa_sm100::kMaxWaitKcycles;
+    px.status = dev->status_ptr;
+    return fa_sm100::launch_combine(nullptr, nullptr, out, lse_out, world, rows, head_dim, dtype, out_fp32,
+                                    static_cast<cudaStream_t>(stream), false, 0, 0, &px);
 }
 
 int fa_mask_fwd_sm100_device_status(int32_t device, uint32_t* status, int32_t clear) {

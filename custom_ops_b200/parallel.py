@@ -11,11 +11,19 @@ Two ways to spread the operator:
 
 * **cross-GPU Split-KV** for the small-grid long-context shape: rank ``g`` owns keys
   ``[g*Sk/G, (g+1)*Sk/G)`` of every head (slice boundaries are multiples of the
-  128-key block), runs the local forward with fp32 output and LSE, the partials are
-  all-gathered over NCCL (about 1 MB per rank: latency-bound on NVLink) and merged
-  by the same log-sum-exp kernel the single-GPU Split-KV uses
-  (``fa_mask_fwd_sm100_combine``).  Data always lands in local HBM through NCCL
-  before a kernel touches it.  :func:`splitkv_forward`.
+  128-key block), runs the local forward with fp32 output and LSE into its packed part
+  (about 1 MB per rank), and the parts are merged by the same log-sum-exp kernel the
+  single-GPU Split-KV uses.  Two ways to exchange the parts (:func:`splitkv_forward`):
+
+  - ``exchange="peer"``: the parts live in symmetric (peer-addressable) memory; the merge
+    kernel itself signals the other ranks, waits -- bounded -- for their parts and reads
+    them straight over NVLink with plain loads.  One kernel does the exchange and the
+    merge; no collective library call sits on the path (a 1 MB NCCL all-gather costs
+    about 20 us of latency, more than a rank's share of the attention itself).
+  - ``exchange="nccl"``: one ``all_gather_into_tensor`` of the parts, then the merge on
+    local memory.  The fallback where symmetric memory cannot be set up.
+
+  No TMA load and no multicast ever touches another GPU's memory.
 """
 from __future__ import annotations
 
@@ -50,15 +58,25 @@ def units_to_slices(lo: int, hi: int, Hk: int) -> List[Tuple[int, int, int]]:
 
 
 def shard_inputs(q, k, v, mask, world: int, rank: int):
-    """This rank's independent sub-problems: a list of ``(q, k, v, mask)`` with batch 1,
-    covering its (batch, kv-head) units.  The mask has no head dimension, so a rank
-    needs only the mask slices of the batches it touches."""
+    """This rank's independent sub-problems: a list of ``(q, k, v, mask)`` covering its
+    (batch, kv-head) units.  Batch elements of which the rank owns every head stay together
+    as one sub-problem (a contiguous view, nothing is copied); a batch element it shares with
+    another rank gives a sub-problem of batch 1 with its heads.  The mask has no head
+    dimension, so a rank needs only the mask slices of the batches it touches."""
     B, H = q.shape[0], q.shape[1]
     Hk = k.shape[1]
     g = H // Hk
     lo, hi = shard_units(B, Hk, world, rank)
     pieces = []
+    run = None            # consecutive batch elements of which this rank owns every head: one launch
     for b, h0, h1 in units_to_slices(lo, hi, Hk):
+        if h0 == 0 and h1 == Hk:
+            run = (run[0], b + 1) if run is not None and run[1] == b else (b, b + 1)
+            if run[0] != b:
+                pieces.pop()
+            pieces.append((q[run[0]:run[1]], k[run[0]:run[1]], v[run[0]:run[1]], mask[run[0]:run[1]]))
+            continue
+        run = None
         pieces.append((q[b:b + 1, h0 * g:h1 * g].contiguous(), k[b:b + 1, h0:h1].contiguous(),
                        v[b:b + 1, h0:h1].contiguous(), mask[b:b + 1].contiguous()))
     return pieces
@@ -104,6 +122,63 @@ class _SplitKVScratch:
         if self.workspace is None or self.workspace.numel() < max(nbytes, 16):
             self.workspace = torch.empty(max(nbytes, 16), dtype=torch.uint8, device=device)
         return self.workspace
+
+
+class _PeerScratch:
+    """Symmetric-memory buffers of the peer exchange, one set per (device, rows, d, group):
+    two part slots (calls alternate, so a rank that is one call ahead never overwrites a part
+    another rank still reads), then ``world`` flag words.  Set up collectively on first use."""
+
+    _cache: dict = {}
+
+    def __init__(self, device, rows: int, d: int, group):
+        import torch.distributed as dist
+        import torch.distributed._symmetric_memory as symm_mem
+
+        world = dist.get_world_size(group)
+        self.part_floats = (rows * (d + 1) + 3) // 4 * 4
+        self.flag_offset = 2 * self.part_floats
+        total = self.flag_offset + max(64, world)
+        self.buf = symm_mem.empty(total, dtype=torch.float32, device=device)
+        self.buf.zero_()
+        group_name = (group or dist.group.WORLD).group_name
+        self.handle = symm_mem.rendezvous(self.buf, group_name)
+        torch.cuda.synchronize(device)
+        dist.barrier(group)                  # every rank's flags are zero before anyone signals
+        self.table = int(self.handle.buffer_ptrs_dev)     # device array of the ranks' buffer bases
+        self.rank = dist.get_rank(group)
+        self.world = world
+        self.seq = 0
+        self.workspace = None
+
+    @classmethod
+    def get(cls, device, rows: int, d: int, group) -> "_PeerScratch":
+        key = (device.type, device.index, rows, d, id(group))
+        if key not in cls._cache:
+            cls._cache[key] = cls(device, rows, d, group)
+        return cls._cache[key]
+
+    def workspace_for(self, nbytes: int, device):
+        if self.workspace is None or self.workspace.numel() < max(nbytes, 16):
+            self.workspace = torch.empty(max(nbytes, 16), dtype=torch.uint8, device=device)
+        return self.workspace
+
+
+_PEER_FAILED = ""          # why the peer exchange could not be set up in this process (then: NCCL)
+
+
+class _SetupError(RuntimeError):
+    pass
+
+
+def peer_exchange_available() -> bool:
+    """Whether torch offers symmetric memory here (the set-up itself may still fail on
+    hardware without peer access; :func:`splitkv_forward` then falls back to NCCL)."""
+    try:
+        import torch.distributed._symmetric_memory  # noqa: F401
+        return torch.cuda.is_available()
+    except Exception:  # noqa: BLE001
+        return False
 
 
 def _check_operands(q, k, v, mask):
@@ -152,16 +227,41 @@ def _combine_cuda(gathered: torch.Tensor, part_floats: int, world: int, rows: in
     return out
 
 
-def splitkv_forward(q, k_local, v_local, mask_local, group=None, *,
+def _splitkv_forward_peer(q, k_local, v_local, mask_local, group):
+    from . import _cabi
+
+    B, H, Sq, d = q.shape
+    rows = B * H * Sq
+    sc = _PeerScratch.get(q.device, rows, d, group)
+    sc.seq += 1
+    slot = sc.seq & 1
+    part = sc.buf[slot * sc.part_floats:(slot + 1) * sc.part_floats]
+    if k_local.shape[2] > 0:
+        _local_partial_cuda(q, k_local, v_local, mask_local, part, sc)
+    else:
+        part[:rows * d].zero_()
+        part[rows * d:rows * (d + 1)].fill_(float("-inf"))
+    out = torch.empty((rows, d), device=q.device, dtype=q.dtype)
+    _cabi.combine_peers(sc.table, slot * sc.part_floats, sc.flag_offset, sc.rank, sc.world, sc.seq,
+                        out.data_ptr(), 0, rows, d,
+                        _cabi.BF16 if q.dtype == torch.bfloat16 else _cabi.FP16, 0,
+                        q.device.index or 0, torch.cuda.current_stream(q.device).cuda_stream)
+    return out.reshape(B, H, Sq, d)
+
+
+def splitkv_forward(q, k_local, v_local, mask_local, group=None, *, exchange: str = "auto",
                     local_fn: Optional[Callable] = None, combine_fn: Optional[Callable] = None):
     """Cross-GPU Split-KV.  ``q`` is replicated; ``k_local``/``v_local``/``mask_local`` hold
     this rank's key slice (see :func:`kv_slice_bounds`), possibly empty.  Every rank
     returns the full result ``(B, H, Sq, d)`` in q's dtype.
 
     Per call: one forward that writes its fp32 result and LSE straight into this rank's packed
-    part, one ``all_gather_into_tensor`` of the parts (rank-major), one merge kernel that reads
-    the gathered parts where they lie.  Nothing is concatenated, copied or allocated in the
-    steady state (the buffers are kept per shape).
+    part, then either the merge kernel with the exchange built in (``exchange="peer"``, the
+    default where symmetric memory is available: parts in peer-addressable memory, read over
+    NVLink by the merge itself) or one ``all_gather_into_tensor`` of the parts and the merge on
+    local memory (``exchange="nccl"``).  Nothing is concatenated, copied or allocated in the
+    steady state (the buffers are kept per shape).  Every rank must make the same sequence of
+    calls.
 
     ``local_fn(q, k, v, mask) -> (O fp32, LSE)`` / ``combine_fn(o_parts, lse_parts, dtype)``
     replace the CUDA entry points in host-logic tests that run on CPU ranks; production
@@ -169,6 +269,20 @@ def splitkv_forward(q, k_local, v_local, mask_local, group=None, *,
     """
     import torch.distributed as dist
 
+    if exchange not in ("auto", "peer", "nccl"):
+        raise ValueError("exchange must be 'auto', 'peer' or 'nccl'")
+    if local_fn is None and combine_fn is None and q.is_cuda and exchange != "nccl":
+        global _PEER_FAILED
+        if exchange == "peer" or (peer_exchange_available() and not _PEER_FAILED):
+            try:
+                return _splitkv_forward_peer(q, k_local, v_local, mask_local, group)
+            except _SetupError:
+                raise
+            except (RuntimeError, AttributeError) as e:
+                # only the collective set-up may fail softly, and it fails on every rank alike
+                if exchange == "peer" or _PeerScratch._cache:
+                    raise
+                _PEER_FAILED = str(e)
     world = dist.get_world_size(group)
     B, H, Sq, d = q.shape
     rows = B * H * Sq

@@ -222,6 +222,24 @@ int fa_mask_fwd_sm100_combine_packed(const float* packed, int64_t part_stride, v
                                      int32_t num_parts, int64_t rows, int32_t head_dim, int32_t dtype,
                                      int32_t out_fp32, int32_t device, void* stream);
 
+/* The same merge with the exchange built in, for ranks (one process per GPU of one box) whose
+ * parts live in peer-addressable ("symmetric") memory: every rank holds a buffer of the same
+ * layout, `part_table` is a DEVICE array of `world` pointers, entry r = the base of rank r's
+ * buffer as this GPU addresses it; a part (layout as for fa_mask_fwd_sm100_combine_packed)
+ * starts `part_offset` floats into a buffer, and `flag_offset` floats into it lie `world` 32-bit
+ * flag words that start at 0.  The kernel stores `seq` (the same on every rank for one call,
+ * growing by one per call, never 0) into word `rank` of every rank's flags, waits until all of
+ * its own words show at least `seq` -- bounded like every wait of this library: after about a
+ * second it gives up, reports through the status word and writes nothing -- and then merges
+ * the parts, reading the other GPUs' memory directly with plain loads (no multicast, no
+ * collective library).  A caller alternates between two part slots from call to call, so that
+ * a rank that is one call ahead never overwrites a part another rank is still reading.
+ * No counterpart in the reference. */
+int fa_mask_fwd_sm100_combine_peers(const void* part_table, int64_t part_offset, int64_t flag_offset,
+                                    int32_t rank, int32_t world, uint32_t seq, void* out, float* lse_out,
+                                    int64_t rows, int32_t head_dim, int32_t dtype, int32_t out_fp32,
+                                    int32_t device, void* stream);
+
 /* Synchronises `device` and returns in *status the sticky device-side status
  * word: 0, or the code of the first bounded wait that ran out.  Clears it when
  * `clear` != 0.  No counterpart in the reference, whose kernels wait unbounded. */

@@ -384,9 +384,19 @@ def test_cross_gpu_splitkv_entry_on_one_rank():
                             device_id=torch.device("cuda", 0))
     try:
         q, k, v, m = _cuda(*make_case(1, 4, 4, 128, 2048, 128, torch.bfloat16, "drop_bias", seed=15))
-        out = parallel.splitkv_forward(q, k, v, m)
+        out = parallel.splitkv_forward(q, k, v, m, exchange="nccl")
         torch.cuda.synchronize()
-        check_against_oracle(out, q, k, v, m, "splitkv_forward")
+        check_against_oracle(out, q, k, v, m, "splitkv_forward, NCCL exchange")
+        if parallel.peer_exchange_available():
+            # the exchange through peer-addressable memory, inside the merge kernel; three calls
+            # so that both part slots and the flag sequence are exercised
+            for _ in range(3):
+                out_p = parallel.splitkv_forward(q, k, v, m, exchange="peer")
+            torch.cuda.synchronize()
+            assert torch.equal(out_p, out)
+            # a sliced (non-contiguous) operand is refused instead of being misread
+            with pytest.raises(ValueError):
+                parallel.splitkv_forward(q, k[:, :, :1024], v[:, :, :1024], m[..., :1024], exchange="nccl")
     finally:
         dist.destroy_process_group()
 
