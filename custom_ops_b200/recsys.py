@@ -326,16 +326,24 @@ class FAOps(CustomOps):
 
 
 class RecsysOps:
-    """Lazy facade over the operator groups (here: only "fa")."""
+    """Lazy facade over the operator groups (here: only "fa").
+
+    The public surface -- ``configure``, ``disable_jit``, ``ensure_loaded``, ``load``, ``groups``,
+    ``is_available``, ``load_error``, ``load_precompiled`` and the operators themselves -- is the
+    reference facade's (``recsys.py:466-656``), because callers and the loader-contract tests use
+    exactly these names, argument meanings and messages.  The bookkeeping behind it is this
+    package's own: one table of group states, every public method a query or a transition on it.
+    """
 
     _GROUP_CLASSES = {"fa": FAOps}
     _OP_TO_GROUP = {"mha_fwd_with_mask": "fa"}
 
     def __init__(self, *, allow_jit: bool = True) -> None:
         self._allow_jit = bool(allow_jit)
-        self._groups: dict = {}
+        self._groups: dict = {}          # name -> CustomOps instance, once somebody asked for it
         self._lock = threading.RLock()
 
+    # ---- policy
     @property
     def allow_jit(self) -> bool:
         return self._allow_jit
@@ -345,46 +353,62 @@ class RecsysOps:
         self.configure(allow_jit=value)
 
     def configure(self, *, allow_jit: bool) -> "RecsysOps":
+        """Sets the build policy for the groups that exist and for those still to come."""
         with self._lock:
             self._allow_jit = bool(allow_jit)
-            for g in self._groups.values():
-                g.configure(allow_jit=allow_jit)
-        return self
+            for inst in list(self._groups.values()):
+                inst.configure(allow_jit=self._allow_jit)
+            return self
 
     def disable_jit(self) -> "RecsysOps":
         return self.configure(allow_jit=False)
 
+    # ---- the table of groups
     def _validate_group(self, name: str) -> None:
         if name not in self._GROUP_CLASSES:
             raise ValueError(f"Unknown group {name!r}; available: {sorted(self._GROUP_CLASSES)}")
 
+    def _peek(self, name: str):
+        """The group's instance if somebody created it already, else None; never creates."""
+        self._validate_group(name)
+        return self._groups.get(name)
+
     def _group(self, name: str) -> CustomOps:
+        """The group's instance, created and loaded on first use (a failed load is kept, not
+        raised: ``is_available`` / ``load_error`` report it, calling an operator raises)."""
         with self._lock:
-            self._validate_group(name)
-            inst = self._groups.get(name)
+            inst = self._peek(name)
             if inst is None:
-                inst = self._GROUP_CLASSES[name](allow_jit=self._allow_jit)
-                self._groups[name] = inst
+                inst = self._groups[name] = self._GROUP_CLASSES[name](allow_jit=self._allow_jit)
                 inst.load()
             return inst
+
+    def _state(self, name: str) -> str:
+        inst = self._groups.get(name)
+        if inst is None:
+            return "not_loaded"
+        return "loaded" if inst.is_available() else "failed"
 
     def load_precompiled(self, group: str = "fa", path: Optional[str] = None,
                          metadata_path: Optional[str] = None) -> "RecsysOps":
         with self._lock:
-            self._validate_group(group)
-            inst = self._groups.get(group) or self._GROUP_CLASSES[group](allow_jit=False)
+            inst = self._peek(group)
+            if inst is None:
+                inst = self._GROUP_CLASSES[group](allow_jit=False)
             inst.load_precompiled(path, metadata_path)
             self._groups[group] = inst
-        return self
+            return self
 
     def ensure_loaded(self, *names) -> "RecsysOps":
-        targets = names if names else tuple(self._GROUP_CLASSES)
+        """Loads the named groups (all of them when none is named); unknown names are refused
+        before anything is loaded."""
+        wanted = list(names) or list(self._GROUP_CLASSES)
         with self._lock:
-            for n in targets:
-                self._validate_group(n)
-            for n in targets:
-                self._group(n)
-        return self
+            for name in wanted:
+                self._validate_group(name)
+            for name in wanted:
+                self._group(name)
+            return self
 
     def load(self) -> "RecsysOps":
         return self.ensure_loaded()
@@ -392,36 +416,27 @@ class RecsysOps:
     @property
     def groups(self) -> dict:
         with self._lock:
-            return {
-                name: ("loaded" if self._groups[name].is_available() else "failed")
-                if name in self._groups else "not_loaded"
-                for name in self._GROUP_CLASSES
-            }
+            return {name: self._state(name) for name in self._GROUP_CLASSES}
 
     def is_available(self, group: Optional[str] = None) -> bool:
+        """One group: whether it is loaded and usable (loading it now unless building is off and
+        nobody loaded it).  No group named: whether everything that was loaded so far works."""
         with self._lock:
-            if group is not None:
-                self._validate_group(group)
-                if not self._allow_jit:
-                    inst = self._groups.get(group)
-                    return inst is not None and inst.is_available()
-                return self._group(group).is_available()
-            if not torch.cuda.is_available():
-                return False
-            if not self._allow_jit and not self._groups:
-                return False
-            return all(i.is_available() for i in self._groups.values())
+            if group is None:
+                if not torch.cuda.is_available() or (not self._allow_jit and not self._groups):
+                    return False
+                return all(state == "loaded" for state in (self._state(n) for n in self._groups))
+            inst = self._peek(group) if not self._allow_jit else self._group(group)
+            return inst is not None and inst.is_available()
 
     def load_error(self, group: Optional[str] = None):
+        """The kept load error of one group, or of the first group that failed."""
         with self._lock:
             if group is not None:
-                self._validate_group(group)
-                inst = self._groups.get(group)
-                return inst.load_error() if inst is not None else None
-            for inst in self._groups.values():
-                if not inst.is_available():
-                    return inst.load_error()
-        return None
+                inst = self._peek(group)
+                return None if inst is None else inst.load_error()
+            failed = [inst for inst in self._groups.values() if not inst.is_available()]
+            return failed[0].load_error() if failed else None
 
     def _dispatch(self, backend, group: str) -> CustomOps:
         _resolve_backend(backend)

@@ -134,6 +134,9 @@ def test_gqa(dtype, case):
     (1, 1, 128, 8192, 64, "zero"), (1, 1, 64, 4096, 64, "causal"),
     (1, 2, 128, 8192, 128, "zero"), (1, 2, 256, 16384, 128, "random"),
     (1, 2, 128, 1032, 128, "random"),
+    # the reference's cross-arch suite at full length (tests/remote_verify_suite.py:126-161):
+    # ragged Sk on the split path
+    (1, 2, 128, 8195, 128, "drop10"), (1, 1, 128, 32773, 128, "drop10"), (1, 2, 64, 16390, 64, "drop10"),
 ])
 def test_splitkv_auto(dtype, case):
     b, h, sq, sk, d, kind = case
@@ -189,6 +192,20 @@ def test_fp32_partial_output_and_merge_entry_point():
     torch.cuda.synchronize()
     assert (merged.float() - full.float()).abs().max() < 4e-3
     check_against_oracle(merged, q, k, v, m, "merged halves")
+    # the same parts packed [O | LSE] at a stride, as an all-gather delivers them
+    stride = rows * 129 + 12                       # padded: a multiple of 4 floats
+    packed = torch.full((2 * stride,), float("nan"), device="cuda", dtype=torch.float32)
+    for s_, (o, l) in enumerate(zip(parts, lses)):
+        packed[s_ * stride:s_ * stride + rows * 128] = o.reshape(-1)
+        packed[s_ * stride + rows * 128:s_ * stride + rows * 129] = l.reshape(-1)
+    merged2 = torch.empty_like(full)
+    _cabi.combine_packed(packed.data_ptr(), stride, merged2.data_ptr(), 0, 2, rows, 128, _cabi.BF16, 0, 0,
+                         torch.cuda.current_stream().cuda_stream)
+    torch.cuda.synchronize()
+    assert torch.equal(merged2, merged)
+    with pytest.raises(_cabi.FaSm100Error) as e:    # parts would overlap
+        _cabi.combine_packed(packed.data_ptr(), rows * 128, merged2.data_ptr(), 0, 2, rows, 128, _cabi.BF16, 0, 0, 0)
+    assert e.value.code == -3
 
 
 # ---------------------------------------------------------------- the five configurations
