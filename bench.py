@@ -315,14 +315,16 @@ def oracle_slice_error(out, q_h, k_h, v_h, m_h, b: int, h: int):
     return float(mx), float(mean)
 
 
-def visited_fraction(w, m_h) -> float:
-    """Share of (256-row query pair, 128-key block) regions that hold a visible key."""
-    mp = -(-w.Sq // 256)
+def visited_fraction(w, m_h, region_rows: int = 256) -> float:
+    """Share of (region_rows query rows, 128-key block) regions that hold a visible key:
+    256-row query pairs, or 128-row tiles where grouped heads run in pairs
+    (``FaMaskFwdPlan.head_pairs``)."""
+    mp = -(-w.Sq // region_rows)
     nb = -(-w.Sk // 128)
     fin = ~torch.isneginf(m_h.float())
-    pad = torch.zeros(m_h.shape[0], 1, mp * 256, nb * 128, dtype=torch.bool)
+    pad = torch.zeros(m_h.shape[0], 1, mp * region_rows, nb * 128, dtype=torch.bool)
     pad[:, :, :w.Sq, :w.Sk] = fin[:, :, :w.Sq, :w.Sk]
-    return float(pad.view(m_h.shape[0], mp, 256, nb, 128).any(dim=4).any(dim=2).float().mean())
+    return float(pad.view(m_h.shape[0], mp, region_rows, nb, 128).any(dim=4).any(dim=2).float().mean())
 
 
 def measure_config(name: str, dev, steps: int, peaks, flush):
@@ -375,7 +377,7 @@ def measure_config(name: str, dev, steps: int, peaks, flush):
     ms = [a.elapsed_time(b) for a, b in zip(starts, ends)]
     mean_ms = sum(ms) / len(ms)
     mx, mean = oracle_slice_error(out, q_h, k_h, v_h, m_h, w.B - 1, w.H - 1)
-    visited = visited_fraction(w, m_h) if plan.tile_skip else 1.0
+    visited = visited_fraction(w, m_h, 128 if plan.head_pairs else 256) if plan.tile_skip else 1.0
     tflops = w.flops / (mean_ms * 1e-3) / 1e12
     gbs = w.bytes / (mean_ms * 1e-3) / 1e9
     if name == "splitkv_long":
@@ -773,7 +775,7 @@ def run_ours(args, w):
         # Tile skipping: the headline value keeps the dense convention (4*B*H*Sq*Sk*d, mask
         # ignored, like the reference's benchmark); the tensor roofline uses the FLOPs of the
         # key blocks that are actually visited.
-        visited_frac = visited_fraction(wl, m_h) if plan.tile_skip else 1.0
+        visited_frac = visited_fraction(wl, m_h, 128 if plan.head_pairs else 256) if plan.tile_skip else 1.0
         hbm_bound = w.name == "splitkv_long"
         if hbm_bound:
             achieved = w_local.bytes / (mean_ms * 1e-3) / 1e9

@@ -12,7 +12,7 @@ import os
 
 from . import build as _build
 
-ABI_VERSION = 1
+ABI_VERSION = 2
 FP16, BF16 = 0, 1
 MAX_SPLITS = 128
 
@@ -81,6 +81,8 @@ class FaMaskFwdPlan(ctypes.Structure):
         ("dual_split", ctypes.c_int32),
         ("tile_skip", ctypes.c_int32),
         ("unit_cut", ctypes.c_int32),
+        ("head_pairs", ctypes.c_int32),
+        ("reserved0", ctypes.c_int32),
         ("workspace_bytes", ctypes.c_uint64),
     ]
 
@@ -164,13 +166,14 @@ def check(code: int):
 
 NO_TILE_SKIP = 1      # FaMaskFwdArgs.disable bits (FA_SM100_NO_*)
 NO_UNIT_CUT = 2
+NO_HEAD_PAIRS = 4
 TEST_STALL_MASK = 0x100   # tests only: withhold the mask loads so that a bounded wait runs out
 
 
 def make_args(*, q=0, k=0, v=0, mask=0, out=0, lse=0, batch, heads, heads_k, seqlen_q, seqlen_k,
               head_dim, dtype, mask_seqlen_q=None, mask_seqlen_k=None, mask_batch_stride=None,
               mask_row_stride=None, device=0, num_splits=0, out_fp32=0,
-              no_tile_skip=0, no_unit_cut=0, test_stall_mask=0) -> FaMaskFwdArgs:
+              no_tile_skip=0, no_unit_cut=0, test_stall_mask=0, no_head_pairs=0) -> FaMaskFwdArgs:
     a = FaMaskFwdArgs()
     a.struct_size = ctypes.sizeof(FaMaskFwdArgs)
     a.device = device
@@ -187,6 +190,7 @@ def make_args(*, q=0, k=0, v=0, mask=0, out=0, lse=0, batch, heads, heads_k, seq
     a.num_splits = num_splits
     a.out_fp32 = out_fp32
     a.disable = ((NO_TILE_SKIP if no_tile_skip else 0) | (NO_UNIT_CUT if no_unit_cut else 0)
+                 | (NO_HEAD_PAIRS if no_head_pairs else 0)
                  | (TEST_STALL_MASK if test_stall_mask else 0))
     return a
 

@@ -122,13 +122,16 @@ struct KParams {
     unsigned int* status;
     int B, H, Hk, Sq, Sk;
     int num_splits, kv_blocks;
-    int m_pairs;              // 256-row query pairs per (batch, head)
-    int total_units;          // B * H * m_pairs * split_groups; a CTA takes every gridDim.x-th one
+    int m_pairs;              // row groups per (batch, head): 256-row query pairs, or 128-row tiles
+                              // with head_pairs
+    int head_pairs;           // 1: the two slots of a unit are two heads of one KV group over the
+                              // SAME 128 query rows (they share every K/V tile and every mask tile)
+    int total_units;          // B * (H or H/2) * m_pairs * split_groups; a CTA takes every gridDim.x-th one
     int split_groups;         // CTAs along the split axis: num_splits, or ceil(num_splits/2) in dual mode
     int dual;                 // 1: one query tile, two KV splits per CTA
     unsigned int* unit_counter;         // with block_flags: units taken beyond the first of each CTA
-    const unsigned char* block_flags;   // (B, m_pairs, kv_blocks): 0 = every key of the block is
-                                        // masked (-inf) for all 256 rows -> skipped; NULL = no skipping
+    const unsigned char* block_flags;   // (B, m_pairs, kv_blocks): 0 = every key of the block is masked
+                                        // (-inf) for all rows of the group -> skipped; NULL = no skipping
     float* cut_part;          // per CTA: [256][D] fp32 O, then per CTA [256] LSE, then per CTA 8 tags
     unsigned long long cut_tag;   // value a softmax warp stores in its tag once its partial is written
     int cut_units;            // P >= 2: units of the last, partial round are done by P CTAs each; 0: whole
@@ -314,6 +317,9 @@ fa_mask_fwd_kernel(const __grid_constant__ CUtensorMap tm_q,
     // groups are still writing the previous unit's output.  Slots of a unit:
     //   pair mode  slot t = query tile t of the pair; both slots walk the same key blocks and
     //              share every K/V tile in shared memory;
+    //   head pairs (pair mode with grouped-query heads, group size even) slot t = head 2u + t
+    //              over the SAME 128 query rows: the slots share the K/V tiles and also the mask
+    //              tile, which is loaded once for both, and key blocks are skipped per 128 rows;
     //   dual mode  (one query tile only, Split-KV; one unit per CTA) slot t = KV split
     //              2*group + t of the SAME query tile: two key ranges stream side by side.
     const bool dual = p.dual != 0;
@@ -332,11 +338,12 @@ fa_mask_fwd_kernel(const __grid_constant__ CUtensorMap tm_q,
         int rest = unit;
         const int sgroup = rest % p.split_groups;
         rest /= p.split_groups;
-        // later query pairs first: under causal-like masks they carry the most key blocks
+        // later query rows first: under causal-like masks they carry the most key blocks
         const int mpair = p.m_pairs - 1 - (rest % p.m_pairs);
         rest /= p.m_pairs;
-        const int h = rest % p.H;
-        const int b = rest / p.H;
+        const int heads_u = p.head_pairs ? (p.H >> 1) : p.H;
+        const int h = p.head_pairs ? 2 * (rest % heads_u) : rest % heads_u;     // head of slot 0
+        const int b = rest / heads_u;
         int count = 0;
         if constexpr (LIST) {
             const unsigned char* fl = p.block_flags +
@@ -354,7 +361,7 @@ fa_mask_fwd_kernel(const __grid_constant__ CUtensorMap tm_q,
         if (lane < 2) {
             // lane t describes slot t
             const int t = lane;
-            const int m0 = mpair * (2 * kBlockM);
+            const int m0 = p.head_pairs ? mpair * kBlockM : mpair * (2 * kBlockM);
             const int split = dual ? 2 * sgroup + t : sgroup;
             // split s owns key blocks [s*nb/S, (s+1)*nb/S): sizes differ by at most one block
             const unsigned nb = static_cast<unsigned>(p.kv_blocks), ns = static_cast<unsigned>(p.num_splits);
@@ -365,7 +372,7 @@ fa_mask_fwd_kernel(const __grid_constant__ CUtensorMap tm_q,
                 begin = part_begin;
                 end = part_begin + part_n;
             }
-            const int row0 = dual ? m0 : m0 + t * kBlockM;
+            const int row0 = (dual || p.head_pairs) ? m0 : m0 + t * kBlockM;
             const bool on = dual ? (split < p.num_splits) : (row0 < p.Sq);
             int n = on ? max(end - begin, 0) : -1;                 // -1: the slot does not exist
             if (LIST && on) n = count;                             // may be 0: nothing visible at all
@@ -400,7 +407,8 @@ fa_mask_fwd_kernel(const __grid_constant__ CUtensorMap tm_q,
         }
         for (int i = 0; i < 4; ++i) {
             mbar_init(bar_m_full + 8 * i, 1);
-            mbar_init(bar_m_empty + 8 * i, kSoftmaxThreads);
+            // (with head pairs both softmax groups read panels 0 and 1)
+            mbar_init(bar_m_empty + 8 * i, (p.head_pairs && i < 2) ? 2 * kSoftmaxThreads : kSoftmaxThreads);
         }
         for (int i = 0; i < NS + 1; ++i) {
             mbar_init(bar_kv_full + 8 * i, 1);
@@ -487,7 +495,8 @@ fa_mask_fwd_kernel(const __grid_constant__ CUtensorMap tm_q,
 #pragma unroll
                             for (int s = 0; s < C::kSub; ++s)
                                 tma_load_3d(sQ + t * TILE + s * SUB, &tm_q, bar_q_full + 8 * t, s * 64,
-                                            ui_get(ui, kUiSlot + 4 * t + kUiRow0), q_plane);
+                                            ui_get(ui, kUiSlot + 4 * t + kUiRow0),
+                                            q_plane + (p.head_pairs ? t : 0));
                         }
                         if (!dual) {
                             // shared by both slots: K_0, V_0, K_1, V_1, ...
@@ -553,6 +562,7 @@ fa_mask_fwd_kernel(const __grid_constant__ CUtensorMap tm_q,
 #pragma unroll
                         for (int t = 0; t < 2; ++t) {
                             if (!ok || j >= n_of[t]) continue;
+                            if (t == 1 && p.head_pairs) continue;      // slot 1 reads slot 0's panels
                             const int blk = LIST ? static_cast<int>(lds16(lst + 2 * j)) : begin_of[t] + j;
 #pragma unroll
                             for (int hf = 0; hf < 2; ++hf) {
@@ -822,7 +832,8 @@ fa_mask_fwd_kernel(const __grid_constant__ CUtensorMap tm_q,
         const uint32_t bar_p2 = bar_p_ready2 + 8 * t;
         // this thread's row inside a swizzled mask panel: 16-byte chunk c of row r
         // lives at r*128 + ((c ^ (r & 7)) << 4)
-        const uint32_t m_row_addr = sM + (2 * t) * kPanelBytes + row_in_tile * 128;
+        const int mt = p.head_pairs ? 0 : t;             // whose mask panels this group reads
+        const uint32_t m_row_addr = sM + (2 * mt) * kPanelBytes + row_in_tile * 128;
         const uint32_t m_xor = static_cast<uint32_t>(row_in_tile & 7) << 4;
         const float2 scale2 = make_float2(p.scale, p.scale);
 
@@ -869,8 +880,8 @@ fa_mask_fwd_kernel(const __grid_constant__ CUtensorMap tm_q,
                 // costs about 150 cycles even when the barrier has long completed, and here that
                 // latency falls into time the thread would spend waiting anyway, so that nothing
                 // but the wake-up from the score barrier stands between S and the first load.
-                bool ok = mbar_wait(dummy ? bar_scratch : bar_m_full + 8 * (2 * t), par, abort_flag, p.status, kStSoftmaxMask);
-                ok = mbar_wait(dummy ? bar_scratch : bar_m_full + 8 * (2 * t + 1), par, abort_flag, p.status, kStSoftmaxMask) && ok;
+                bool ok = mbar_wait(dummy ? bar_scratch : bar_m_full + 8 * (2 * mt), par, abort_flag, p.status, kStSoftmaxMask);
+                ok = mbar_wait(dummy ? bar_scratch : bar_m_full + 8 * (2 * mt + 1), par, abort_flag, p.status, kStSoftmaxMask) && ok;
                 ok = mbar_wait(dummy ? bar_scratch : bar_s, par, abort_flag, p.status, kStSoftmaxS) && ok;
                 if (!__all_sync(0xffffffffu, ok)) { alive = false; break; }
                 tc_fence_after();
@@ -913,7 +924,7 @@ fa_mask_fwd_kernel(const __grid_constant__ CUtensorMap tm_q,
                             mt1 = max3(mt1, xa.y, xb.y);
                         }
                     }
-                    mbar_arrive(dummy ? bar_scratch : bar_m_empty + 8 * (2 * t + pn));      // panel may be refilled
+                    mbar_arrive(dummy ? bar_scratch : bar_m_empty + 8 * (2 * mt + pn));      // panel may be refilled
                 }
                 const float mt = fmaxf(mt0, mt1);
 
@@ -976,7 +987,8 @@ fa_mask_fwd_kernel(const __grid_constant__ CUtensorMap tm_q,
             // holds no registers during the loop above
             const int row = ui_get(ui, kUiSlot + 4 * t + kUiRow0) + row_in_tile;
             const bool row_ok = row < p.Sq;
-            const int u_b = ui_get(ui, kUiB), u_h = ui_get(ui, kUiH), u_sgroup = ui_get(ui, kUiSgroup);
+            const int u_b = ui_get(ui, kUiB), u_sgroup = ui_get(ui, kUiSgroup);
+            const int u_h = ui_get(ui, kUiH) + (p.head_pairs ? t : 0);
             const int split_t = ui_get(ui, kUiSlot + 4 * t + kUiSplit);
             const int n_other = ui_get(ui, kUiSlot + 4 * (t ^ 1) + kUiN);
             const int part = ui_get(ui, kUiPart);
@@ -1431,7 +1443,7 @@ __device__ unsigned int g_skip_ticket = 0;
 __global__ void __launch_bounds__(256)
 fa_mask_classify_kernel(const uint16_t* __restrict__ mask, long long bs, long long rs, int Sq, int Sk,
                         uint32_t neg_inf2, unsigned char* __restrict__ flags, int* hint,
-                        unsigned int* unit_counter) {
+                        unsigned int* unit_counter, int region_rows) {
     const int nt = blockIdx.x, mp = blockIdx.y, b = blockIdx.z;
     pdl_wait_prior_grid();                          // a re-pitch kernel may have written the mask
     pdl_launch_dependents();
@@ -1442,16 +1454,17 @@ fa_mask_classify_kernel(const uint16_t* __restrict__ mask, long long bs, long lo
     const int col = nt * kBlockN + vec * 8;
     const uint16_t neg_inf = static_cast<uint16_t>(neg_inf2 & 0xffffu);
     int visible = 0;
-    // 16 passes of 16 rows in two rounds: 4 passes, a block-wide vote (a region with anything
-    // visible usually ends here), then the other 12 with all their loads in flight at once.
-    // (One pass per vote made a fully masked region cost 16 round trips to memory.)
+    // A region is `region_rows` = 256 rows (a query pair) or 128 rows (a tile shared by a pair of
+    // heads) of one key block.  Passes of 16 rows in two rounds: 4 passes, a block-wide vote (a
+    // region with anything visible usually ends here), then the others with all their loads in
+    // flight at once.  (One pass per vote made a fully masked region cost 16 round trips to memory.)
     auto scan = [&](auto passes_tag, int pass0) {
         constexpr int kPasses = decltype(passes_tag)::value;
         uint4 v[kPasses];
         bool in[kPasses];
 #pragma unroll
         for (int u = 0; u < kPasses; ++u) {
-            const int row = mp * 2 * kBlockM + (pass0 + u) * 16 + rsub;
+            const int row = mp * region_rows + (pass0 + u) * 16 + rsub;
             in[u] = row < Sq && col < Sk;
             v[u] = make_uint4(neg_inf2, neg_inf2, neg_inf2, neg_inf2);
             if (in[u]) v[u] = __ldg(reinterpret_cast<const uint4*>(mask + b * bs + row * rs + col));
@@ -1474,7 +1487,8 @@ fa_mask_classify_kernel(const uint16_t* __restrict__ mask, long long bs, long lo
     scan(std::integral_constant<int, 4>{}, 0);
     visible = __syncthreads_or(visible) ? 1 : 0;
     if (!visible) {
-        scan(std::integral_constant<int, 12>{}, 4);
+        if (region_rows > kBlockM) scan(std::integral_constant<int, 12>{}, 4);
+        else scan(std::integral_constant<int, 4>{}, 4);
         visible = __syncthreads_or(visible) ? 1 : 0;
     }
     if (threadIdx.x == 0) {
@@ -1722,7 +1736,7 @@ static int make_plan(const FaMaskFwdArgs* a, FaMaskFwdPlan* plan) {
     query_device(a->device, &dev);
     std::memset(plan, 0, sizeof(*plan));
     const int d = a->head_dim;
-    const int m_pairs = ceil_div(a->seqlen_q, 2 * kBlockM);
+    int m_pairs = ceil_div(a->seqlen_q, 2 * kBlockM);
     const int nb = ceil_div(a->seqlen_k, kBlockN);
     const long long base_ctas = static_cast<long long>(m_pairs) * a->heads * a->batch;
     int splits = 1;
@@ -1754,16 +1768,24 @@ static int make_plan(const FaMaskFwdArgs* a, FaMaskFwdPlan* plan) {
     const int bps = nb > 0 ? ceil_div(nb, splits) : 0;
     const bool dual = one_tile && splits > 1;
     const int split_groups = dual ? ceil_div(splits, 2) : splits;
+    // Grouped-query heads with an even group size: a unit is two heads of one group over one
+    // 128-row tile instead of one head over two tiles.  K/V traffic is the same, every mask
+    // tile is fetched once for two heads, and key blocks are skipped per 128 rows.
+    const bool head_pairs = !dual && (a->heads / a->heads_k) % 2 == 0 &&
+                            (a->disable & FA_SM100_NO_HEAD_PAIRS) == 0;
+    if (head_pairs) m_pairs = ceil_div(a->seqlen_q, kBlockM);
+    const int heads_u = head_pairs ? a->heads / 2 : a->heads;
     plan->num_splits = splits;
     plan->kv_blocks = nb;
     plan->blocks_per_split = bps;
-    plan->q_tiles_per_cta = a->seqlen_q > kBlockM ? 2 : 1;
+    plan->q_tiles_per_cta = (a->seqlen_q > kBlockM || head_pairs) ? 2 : 1;
+    plan->head_pairs = head_pairs ? 1 : 0;
     // Units of (split, 256-row query pair, head, batch).  Pair mode is persistent: one CTA per
     // SM takes every grid_x-th unit, so the loads and the first MMA of a unit run under the
     // previous unit's epilogue.  Dual mode runs one unit per CTA.  (Splitting the units of a
     // half-empty last round into single-tile CTAs was measured and gains nothing: a CTA's time
     // is set by the per-tile softmax -> MMA dependency chain, not by how many tiles it holds.)
-    const long long units = static_cast<long long>(m_pairs) * split_groups * a->heads * a->batch;
+    const long long units = static_cast<long long>(m_pairs) * split_groups * heads_u * a->batch;
     if (units > 0x3fffffffLL) return FA_SM100_ERR_SHAPE;
     plan->grid_x = static_cast<int32_t>((dual || units < dev->sm_count) ? units : dev->sm_count);
     plan->grid_y = 1;
@@ -2209,9 +2231,11 @@ static int forward(const FaMaskFwdArgs* a, void* workspace, size_t workspace_byt
     if (run_classify) {
         unsigned char* flags = ws + (plan.mask_repitched
             ? align256(static_cast<size_t>(a->batch) * a->seqlen_q * ((a->seqlen_k + 7) & ~7) * 2) : 0);
+        const int region_rows = plan.head_pairs ? kBlockM : 2 * kBlockM;
+        const int regions = ceil_div(a->seqlen_q, region_rows);
         unsigned int* unit_counter = reinterpret_cast<unsigned int*>(
-            flags + align256(static_cast<size_t>(a->batch) * ceil_div(a->seqlen_q, 2 * kBlockM) * plan.kv_blocks));
-        const dim3 cgrid(plan.kv_blocks, ceil_div(a->seqlen_q, 2 * kBlockM), a->batch);
+            flags + align256(static_cast<size_t>(a->batch) * regions * plan.kv_blocks));
+        const dim3 cgrid(plan.kv_blocks, regions, a->batch);
         const uint32_t ninf = a->dtype == FA_SM100_BF16 ? 0xFF80FF80u : 0xFC00FC00u;
         cudaLaunchConfig_t cfg = {};
         cfg.gridDim = cgrid;
@@ -2223,7 +2247,7 @@ static int forward(const FaMaskFwdArgs* a, void* workspace, size_t workspace_byt
         cfg.attrs = attr;
         cfg.numAttrs = plan.mask_repitched ? 1 : 0;      // chained behind the re-pitch kernel
         if (cudaLaunchKernelEx(&cfg, fa_mask_classify_kernel, mask_ptr, mask_bs, mask_rs, a->seqlen_q,
-                               a->seqlen_k, ninf, flags, hint_counter, unit_counter) != cudaSuccess) {
+                               a->seqlen_k, ninf, flags, hint_counter, unit_counter, region_rows) != cudaSuccess) {
             return cuda_failed(__LINE__);
         }
         ++g_launches;
@@ -2238,10 +2262,11 @@ static int forward(const FaMaskFwdArgs* a, void* workspace, size_t workspace_byt
     kp.B = a->batch; kp.H = a->heads; kp.Hk = a->heads_k; kp.Sq = a->seqlen_q; kp.Sk = a->seqlen_k;
     kp.num_splits = plan.num_splits;
     kp.kv_blocks = plan.kv_blocks;
-    kp.m_pairs = ceil_div(a->seqlen_q, 2 * kBlockM);
+    kp.head_pairs = plan.head_pairs;
+    kp.m_pairs = plan.head_pairs ? ceil_div(a->seqlen_q, kBlockM) : ceil_div(a->seqlen_q, 2 * kBlockM);
     kp.dual = plan.dual_split;
     kp.split_groups = plan.dual_split ? ceil_div(plan.num_splits, 2) : plan.num_splits;
-    kp.total_units = kp.m_pairs * kp.split_groups * a->heads * a->batch;
+    kp.total_units = kp.m_pairs * kp.split_groups * (plan.head_pairs ? a->heads / 2 : a->heads) * a->batch;
     if (plan.unit_cut) {
         uint8_t* slots = static_cast<uint8_t*>(workspace) + plan.workspace_bytes - cut_bytes(plan.grid_x, d);
         // the partials are written with 256-bit stores; a workspace that is only 16-byte

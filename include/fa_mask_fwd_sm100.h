@@ -33,7 +33,7 @@
 extern "C" {
 #endif
 
-#define FA_SM100_ABI_VERSION 1
+#define FA_SM100_ABI_VERSION 2
 
 enum {
     FA_SM100_OK = 0,
@@ -57,6 +57,8 @@ enum {
     FA_SM100_NO_TILE_SKIP = 1,  /* visit every key block even where the mask hides it entirely */
     FA_SM100_NO_UNIT_CUT = 2,   /* every (query pair, head, batch) unit is finished by one CTA, so the
                                  * result does not depend on the number of SMs */
+    FA_SM100_NO_HEAD_PAIRS = 4, /* grouped-query heads are not paired: a unit is one head over a 256-row
+                                 * query pair, as for ungrouped heads */
     FA_SM100_TEST_STALL_MASK = 0x100  /* tests only: the kernel's mask loads are withheld and its waits
                                  * get a short limit (FA_SM100_TEST_WAIT_KCYCLES in the environment,
                                  * units of 1024 SM cycles, default 2000), so that a wait runs out,
@@ -130,6 +132,10 @@ typedef struct FaMaskFwdPlan {
                                  * of the last, partial round are done by P <= SMs / R CTAs each (one
                                  * piece of the key blocks per CTA, merged through the workspace)
                                  * instead of leaving most SMs idle; 0: every unit is done by one CTA */
+    int32_t head_pairs;         /* 1: grouped-query heads with an even group size: a unit is two heads of
+                                 * one KV group over one 128-row query tile (they share every K/V tile
+                                 * and every mask tile, and key blocks are skipped per 128 rows) */
+    int32_t reserved0;
     uint64_t workspace_bytes;
 } FaMaskFwdPlan;
 

@@ -128,6 +128,23 @@ def test_gqa(dtype, case):
     check_against_oracle(out, q, k, v, m, f"gqa{case}")
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("case", [(2, 8, 2, 300, 700, 128, "drop_bias", 0), (1, 4, 2, 1000, 1411, 64, "causal", 0),
+                                  (3, 12, 6, 128, 256, 128, "random", 0), (1, 16, 4, 77, 1500, 128, "block", 1),
+                                  (1, 8, 4, 640, 2048, 128, "drop10", 3), (2, 4, 1, 129, 130, 64, "all_masked_row", 0)])
+def test_head_pairs_equal_single_heads(dtype, case):
+    """Grouped-query heads with an even group size run as units of two heads over one 128-row
+    tile (one mask tile in shared memory serves both).  Every row still sees its key blocks in the
+    same order, so the result is bit-identical to the run with one head per unit."""
+    b, h, hk, sq, sk, d, kind, splits = case
+    q, k, v, m = _cuda(*make_case(b, h, hk, sq, sk, d, dtype, kind, seed=31))
+    out, lse, plan = run_cabi(q, k, v, m, want_lse=True, num_splits=splits)
+    out1, lse1, plan1 = run_cabi(q, k, v, m, want_lse=True, num_splits=splits, no_head_pairs=1)
+    assert plan.head_pairs == 1 and plan1.head_pairs == 0
+    assert torch.equal(out, out1) and torch.equal(lse, lse1)
+    check_against_oracle(out, q, k, v, m, f"head_pairs{case}")
+
+
 # ---------------------------------------------------------------- split-KV
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("case", [

@@ -27,9 +27,9 @@ def test_library_exports_every_declared_symbol():
 
 
 def test_struct_sizes_match_header_layout():
-    # 2*4 + 6*8 + 8*4 + 2*8 + 4*4 = 120 ; 14*4 + 8 = 64
+    # 2*4 + 6*8 + 8*4 + 2*8 + 4*4 = 120 ; 16*4 + 8 = 72
     assert ctypes.sizeof(_cabi.FaMaskFwdArgs) == 120
-    assert ctypes.sizeof(_cabi.FaMaskFwdPlan) == 64
+    assert ctypes.sizeof(_cabi.FaMaskFwdPlan) == 72
     a = _cabi.make_args(batch=1, heads=1, heads_k=1, seqlen_q=8, seqlen_k=8, head_dim=64,
                         dtype=_cabi.BF16)
     a.struct_size = 64
@@ -84,6 +84,26 @@ def test_plan_of_the_five_configurations():
     p = _plan(batch=2, heads=4, heads_k=4, seqlen_q=256, seqlen_k=256, head_dim=64)
     assert p.num_splits == 1 and p.grid_x == 8 and p.tile_skip == 0
     assert p.smem_bytes <= 232448
+
+
+def test_plan_pairs_grouped_query_heads():
+    """An even group size: a unit is two heads of a KV group over one 128-row tile; the block flags
+    of the tile-skip pre-pass are then per 128 rows."""
+    sm = _plan().sm_count
+    p = _plan(batch=4, heads=16, heads_k=4, seqlen_q=2048, seqlen_k=2048)
+    assert p.head_pairs == 1 and p.q_tiles_per_cta == 2 and p.grid_x == min(4 * 8 * 16, sm)
+    q = _plan(batch=4, heads=16, heads_k=4, seqlen_q=2048, seqlen_k=2048, no_head_pairs=1)
+    assert q.head_pairs == 0 and q.grid_x == p.grid_x
+    # flags: 4 batches x 16 tiles x 16 key blocks against 4 x 8 pairs x 16
+    assert p.workspace_bytes - q.workspace_bytes == 4 * 16 * 16 - 4 * 8 * 16
+    assert _plan(batch=1, heads=6, heads_k=2, seqlen_q=300, seqlen_k=300).head_pairs == 0      # group of 3
+    assert _plan(batch=1, heads=8, heads_k=8, seqlen_q=300, seqlen_k=300).head_pairs == 0      # no groups
+    # one query tile and few heads: two heads fill the two slots of a CTA
+    p = _plan(batch=2, heads=8, heads_k=2, seqlen_q=100, seqlen_k=256)
+    assert p.head_pairs == 1 and p.grid_x == 2 * 4 and p.q_tiles_per_cta == 2
+    # one query tile with a split key range keeps two splits per CTA instead
+    p = _plan(batch=1, heads=16, heads_k=4, seqlen_q=128, seqlen_k=32768)
+    assert p.dual_split == 1 and p.head_pairs == 0
 
 
 def test_plan_split_rules():
