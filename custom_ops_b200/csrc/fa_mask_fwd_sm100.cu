@@ -392,7 +392,11 @@ fa_mask_fwd_kernel(const __grid_constant__ CUtensorMap tm_q,
             }
         }
     };
-    if (!LIST && warp == 11) publish_unit(0, static_cast<int>(blockIdx.x), kPartWhole, 0, p.kv_blocks, 0);
+    // (The first unit of a CTA is unit blockIdx.x, whole, and can be decoded before the set-up
+    // barrier - unless the launch has fewer units than CTAs, where every unit is cut in pieces.)
+    const bool first_unit_whole = !(p.cut_units != 0 && p.total_units < static_cast<int>(gridDim.x));
+    if (!LIST && first_unit_whole && warp == 11)
+        publish_unit(0, static_cast<int>(blockIdx.x), kPartWhole, 0, p.kv_blocks, 0);
 
     if (warp == kTmaWarp && lane == 0) {
         for (int t = 0; t < 2; ++t) {
@@ -650,7 +654,7 @@ fa_mask_fwd_kernel(const __grid_constant__ CUtensorMap tm_q,
                     }
                     break;
                 }
-                if (LIST || k > 0) publish_unit(k, unit, part, part_begin, part_n, peer_last);
+                if (LIST || k > 0 || !first_unit_whole) publish_unit(k, unit, part, part_begin, part_n, peer_last);
                 __syncwarp();
                 if (lane == 0) mbar_arrive(bar_unit_full + 8 * (k & 1));    // release: board and list visible
             }
@@ -1743,9 +1747,14 @@ static int make_plan(const FaMaskFwdArgs* a, FaMaskFwdPlan* plan) {
     if (nb > 0 && base_ctas > 0) {
         if (a->num_splits > 0) {
             splits = a->num_splits;
-        } else if (base_ctas * 5 < static_cast<long long>(dev->sm_count) * 4 && nb >= 8) {
+        } else if (base_ctas * 5 < static_cast<long long>(dev->sm_count) * 4 &&
+                   nb >= (a->seqlen_q <= kBlockM ? 8 : 24)) {
             // Too few CTAs to fill the GPU: cut the key range so that about one CTA
-            // lands on every SM, keeping at least four key blocks per CTA.
+            // lands on every SM, keeping at least four key blocks per CTA.  (With more than
+            // one query tile a split costs a partial of 256 rows per CTA and a merge kernel
+            // over all of them, about ten key blocks' time: measured, 64 units of 16 key
+            // blocks take 52 us in two splits, 47 us whole and 45 us cut in two pieces that
+            // the kernel merges itself - see unit_cut below - so short key ranges are not split.)
             const long long by_fill = dev->sm_count / base_ctas;
             const long long by_work = nb / 4;
             long long s = by_fill < by_work ? by_fill : by_work;
@@ -1815,14 +1824,22 @@ static int make_plan(const FaMaskFwdArgs* a, FaMaskFwdPlan* plan) {
     // are done in P pieces by P CTAs each.  A piece costs an epilogue of its own and the first
     // piece about 1.5 key blocks' time per partial it merges (measured), so the piece count
     // that pays is about sqrt(0.65 nb), and below six key blocks none does.
+    // The same holds for a launch with fewer units than SMs, whose only round is a partial one
+    // (a (batch, head) shard of a strong-scaled problem, a small batch): then every unit is cut
+    // and the grid grows to units x pieces.
+    // There a piece has to pay for itself against the whole unit, not against an idle SM: not
+    // below twelve key blocks.
     plan->unit_cut = 0;
-    if (!dual && splits == 1 && nb >= 6 && units > dev->sm_count && units % dev->sm_count != 0 &&
-        (a->disable & FA_SM100_NO_UNIT_CUT) == 0) {
+    if (!dual && splits == 1 && nb >= (units < dev->sm_count ? 12 : 6) && units > 0 &&
+        units % dev->sm_count != 0 && (a->disable & FA_SM100_NO_UNIT_CUT) == 0) {
         long long pieces = dev->sm_count / (units % dev->sm_count);
         long long best = 2;
         while ((best + 1) * (best + 1) * 100 <= 65LL * nb) ++best;     // floor(sqrt(0.65 nb)), at least 2
         if (pieces > best) pieces = best;
-        if (pieces >= 2) plan->unit_cut = static_cast<int32_t>(pieces);
+        if (pieces >= 2) {
+            plan->unit_cut = static_cast<int32_t>(pieces);
+            if (units < dev->sm_count) plan->grid_x = static_cast<int32_t>(units * pieces);
+        }
     }
     if (plan->unit_cut) ws += cut_bytes(plan->grid_x, d);
     plan->workspace_bytes = ws;

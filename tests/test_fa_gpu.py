@@ -479,6 +479,29 @@ def test_units_of_the_last_round_are_cut(case):
     assert torch.equal(out_again, out_cut)
 
 
+@pytest.mark.parametrize("case", [(1, 8, 8, 2048, 2048, 128, torch.bfloat16),       # 64 units, two pieces each
+                                  (1, 6, 2, 700, 3000, 64, torch.float16),        # 18 units, three pieces each
+                                  (2, 4, 2, 300, 1500, 128, torch.bfloat16),      # 12 units of two heads
+                                  (1, 1, 1, 100, 5000, 128, torch.float16)])      # (forced single pass) one unit
+def test_fewer_units_than_sms_are_cut_too(case):
+    """A launch whose only round is a partial one - a (batch, head) shard of a strong-scaled problem,
+    a small batch - cuts every unit in pieces and launches units x pieces CTAs."""
+    b, h, hk, sq, sk, d, dtype = case
+    q, k, v, m = _cuda(*make_case(b, h, hk, sq, sk, d, dtype, "drop_bias", seed=29))
+    out_cut, lse_cut, plan = run_cabi(q, k, v, m, want_lse=True, no_tile_skip=1, num_splits=1)
+    out_whole, lse_whole, plan_whole = run_cabi(q, k, v, m, want_lse=True, no_tile_skip=1, no_unit_cut=1,
+                                                num_splits=1)
+    assert plan.unit_cut >= 2 and plan_whole.unit_cut == 0
+    assert plan.grid_x == plan_whole.grid_x * plan.unit_cut and plan.grid_x <= plan.sm_count
+    check_against_oracle(out_cut, q, k, v, m, f"small_cut{case}")
+    assert (out_cut.float() - out_whole.float()).abs().max().item() <= 4e-3
+    assert torch.allclose(lse_cut, lse_whole, atol=1e-4, rtol=1e-5)
+    # with the tile-skip list (no cutting there) the grid is the same and the extra CTAs leave at once
+    out_list, _, plan_list = run_cabi(q, k, v, m, want_lse=True, num_splits=1)
+    assert plan_list.grid_x == plan.grid_x
+    check_against_oracle(out_list, q, k, v, m, f"small_cut_list{case}")
+
+
 def test_unit_cut_survives_cuda_graph_replay():
     """A captured launch repeats its tag on every replay; the head pieces take the tags back
     after reading, so a replay on new data must not pick up the previous replay's partials."""
@@ -526,8 +549,9 @@ def test_tile_skipping_is_exact_on_structured_masks(dtype, case):
     m = torch.zeros(sq, sk).masked_fill(~vis, float("-inf")).to(dtype)
     m = m.view(1, 1, sq, sk).expand(b, 1, sq, sk).contiguous()
     q, k, v, m = _cuda(q, k, v, m)
-    out_skip, lse_skip, plan = run_cabi(q, k, v, m, want_lse=True, num_splits=1)
-    out_all, lse_all, plan_all = run_cabi(q, k, v, m, want_lse=True, num_splits=1, no_tile_skip=1)
+    # (units whole in both runs: cutting a unit in pieces changes the rounding, not skipping)
+    out_skip, lse_skip, plan = run_cabi(q, k, v, m, want_lse=True, num_splits=1, no_unit_cut=1)
+    out_all, lse_all, plan_all = run_cabi(q, k, v, m, want_lse=True, num_splits=1, no_tile_skip=1, no_unit_cut=1)
     assert plan.tile_skip == 1 and plan_all.tile_skip == 0
     assert torch.equal(out_skip, out_all)
     assert torch.equal(lse_skip, lse_all)

@@ -297,5 +297,12 @@ def test_plan_unit_cut_rule():
     assert cut(2 * sm, 128 * 16) == 0                    # whole rounds only
     assert cut(sm + 1, 128 * 5) == 0                     # too few key blocks to pay
     assert cut(sm + 1, 128 * 16, no_unit_cut=1) == 0
-    assert cut(sm - 1, 128 * 16) == 0                    # fewer units than SMs: nothing to cut
+    assert cut(sm - 1, 128 * 16) == 0                    # one piece per CTA is all there is
+    # fewer units than SMs: the only round is a partial one, every unit is cut, the grid grows
+    # (key ranges of 24 blocks and more are split over CTAs instead, see test_plan_split_rules)
+    assert cut(sm // 2, 128 * 16) == 2 and cut(sm // 3, 128 * 20) == 3 and cut(sm // 2, 128 * 11) == 0
+    p = _plan(batch=1, heads=sm // 2, heads_k=sm // 2, seqlen_q=256, seqlen_k=128 * 16)
+    assert p.grid_x == 2 * (sm // 2)
+    assert _plan(batch=1, heads=sm // 2, heads_k=sm // 2, seqlen_q=256, seqlen_k=128 * 16,
+                 no_unit_cut=1).grid_x == sm // 2
 
