@@ -617,7 +617,8 @@ def run_ours(args, w):
             raise SystemExit("--scaling strong: this rank's units span several batch elements or none; "
                              "use a rank count that divides the (batch, kv-head) units of one batch element")
         q_h, k_h, v_h, m_h = pieces[0]
-        w_local = type(w)(w.name, 1, q_h.shape[1], k_h.shape[1], w.Sq, w.Sk, w.d, w.dtype, w.mask_kind, w.sigma)
+        w_local = type(w)(w.name, q_h.shape[0], q_h.shape[1], k_h.shape[1], w.Sq, w.Sk, w.d, w.dtype, w.mask_kind,
+                          w.sigma)
     elif cross_split:
         from custom_ops_b200 import parallel
         lo, hi = parallel.kv_slice_bounds(w.Sk, world, rank)
