@@ -378,6 +378,28 @@ def measure_config(name: str, dev, steps: int, peaks, flush):
     mean_ms = sum(ms) / len(ms)
     mx, mean = oracle_slice_error(out, q_h, k_h, v_h, m_h, w.B - 1, w.H - 1)
     visited = visited_fraction(w, m_h, 128 if plan.head_pairs else 256) if plan.tile_skip else 1.0
+    # The same steps for a caller that vouches for the mask's content (FaMaskFwdArgs.mask_version):
+    # the tile-skip pre-pass then runs once, not per call.
+    remembered = None
+    if plan.tile_skip and not plan.mask_repitched and not rotate:
+        vargs = _cabi.make_args(q=q.data_ptr(), k=k.data_ptr(), v=v.data_ptr(), mask=m.data_ptr(),
+                                out=out.data_ptr(), batch=w.B, heads=w.H, heads_k=w.Hk, seqlen_q=w.Sq,
+                                seqlen_k=w.Sk, head_dim=w.d, dtype=dt, device=dev.index, mask_version=1)
+        for _ in range(4):
+            flush.zero_()
+            _cabi.forward(vargs, ws.data_ptr(), nbytes, stream.cuda_stream)
+        torch.cuda.synchronize(dev)
+        l0 = _cabi.launch_count()
+        for i in range(steps):
+            flush.zero_()
+            starts[i].record(stream)
+            _cabi.forward(vargs, ws.data_ptr(), nbytes, stream.cuda_stream)
+            ends[i].record(stream)
+        torch.cuda.synchronize(dev)
+        vms = [a.elapsed_time(b) for a, b in zip(starts, ends)]
+        vmx, _ = oracle_slice_error(out, q_h, k_h, v_h, m_h, w.B - 1, w.H - 1)
+        remembered = {"us": sum(vms) / len(vms) * 1e3, "us_min": min(vms) * 1e3,
+                      "kernels_per_step": (_cabi.launch_count() - l0) / steps, "max_abs_vs_oracle": vmx}
     tflops = w.flops / (mean_ms * 1e-3) / 1e12
     gbs = w.bytes / (mean_ms * 1e-3) / 1e9
     if name == "splitkv_long":
@@ -391,7 +413,8 @@ def measure_config(name: str, dev, steps: int, peaks, flush):
             "unit": unit, "peak": peak, "frac": achieved / peak, "visited_block_fraction": visited,
             "max_abs_vs_oracle": mx, "mean_abs_vs_oracle": mean, "oracle_slice": f"batch {w.B - 1}, head {w.H - 1}",
             "steps": steps, "kernels_per_step": launches / steps, "num_splits": plan.num_splits,
-            "grid": plan.grid_x, "mask_repitched": bool(plan.mask_repitched),
+            "grid": plan.grid_x, "mask_repitched": bool(plan.mask_repitched), "head_pairs": bool(plan.head_pairs),
+            "with_mask_version": remembered,
             "l2": "4 rotating input copies" if rotate else "256 MB zero-fill before every step"}
 
 

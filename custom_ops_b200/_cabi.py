@@ -62,6 +62,7 @@ class FaMaskFwdArgs(ctypes.Structure):
         ("num_splits", ctypes.c_int32),
         ("out_fp32", ctypes.c_int32),
         ("disable", ctypes.c_int32),
+        ("mask_version", ctypes.c_uint64),
     ]
 
 
@@ -173,7 +174,7 @@ TEST_STALL_MASK = 0x100   # tests only: withhold the mask loads so that a bounde
 def make_args(*, q=0, k=0, v=0, mask=0, out=0, lse=0, batch, heads, heads_k, seqlen_q, seqlen_k,
               head_dim, dtype, mask_seqlen_q=None, mask_seqlen_k=None, mask_batch_stride=None,
               mask_row_stride=None, device=0, num_splits=0, out_fp32=0,
-              no_tile_skip=0, no_unit_cut=0, test_stall_mask=0, no_head_pairs=0) -> FaMaskFwdArgs:
+              no_tile_skip=0, no_unit_cut=0, test_stall_mask=0, no_head_pairs=0, mask_version=0) -> FaMaskFwdArgs:
     a = FaMaskFwdArgs()
     a.struct_size = ctypes.sizeof(FaMaskFwdArgs)
     a.device = device
@@ -192,6 +193,7 @@ def make_args(*, q=0, k=0, v=0, mask=0, out=0, lse=0, batch, heads, heads_k, seq
     a.disable = ((NO_TILE_SKIP if no_tile_skip else 0) | (NO_UNIT_CUT if no_unit_cut else 0)
                  | (NO_HEAD_PAIRS if no_head_pairs else 0)
                  | (TEST_STALL_MASK if test_stall_mask else 0))
+    a.mask_version = mask_version
     return a
 
 

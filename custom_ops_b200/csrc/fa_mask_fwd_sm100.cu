@@ -2171,6 +2171,129 @@ static bool want_classify(const FaMaskFwdArgs* a, const void* mask, long long bs
     return true;
 }
 
+// ---------------------------------------------------------------------------------
+// Block flags remembered across calls (FaMaskFwdArgs.mask_version != 0)
+// ---------------------------------------------------------------------------------
+// The pre-pass reads the whole mask again on every call although many callers present the same
+// mask over and over (every layer of a model, every step of a benchmark).  The library cannot
+// know that a buffer's content is unchanged, so it remembers flags only for callers that vouch
+// for it with a version number they change when the content changes.  The flags live in a
+// small static device array (no allocation), a handful of slots handed out round robin; each
+// slot remembers its key, the stream and an event of the launch that filled it (a hit on
+// another stream waits for that event), and an event of the last launch that read it (a slot
+// is overwritten only behind that).  The pre-pass also tallies the regions it found skippable
+// into a pinned host word: once that has arrived and says "none", hits run the plain kernel.
+constexpr int kFlagSlots = 8;
+constexpr size_t kFlagSlotBytes = 64 * 1024;
+static __device__ __align__(256) unsigned char g_flag_cache[kFlagSlots][kFlagSlotBytes];
+struct FlagEntry {
+    const void* mask = nullptr;
+    long long bs = 0, rs = 0;
+    int B = 0, Sq = 0, Sk = 0, dtype = 0, device = 0, region_rows = 0;
+    unsigned long long version = 0;
+    bool valid = false;
+    cudaStream_t fill_stream = nullptr;
+    cudaEvent_t filled = nullptr, last_read = nullptr;
+    bool read_recorded = false;
+};
+static FlagEntry g_flag_entries[kFlagSlots];
+static int g_flag_next = 0;
+static int* g_flag_tally = nullptr;           // kFlagSlots ints, pinned + mapped
+static void* g_flag_cache_addr[kMaxDevices] = {};
+static std::mutex g_flag_mutex;
+
+enum : int { kFlagsOff = 0, kFlagsFill = 1, kFlagsHit = 2, kFlagsHitNothing = 3 };
+// Looks the key up.  kFlagsFill: *flags is a slot the caller must fill with the pre-pass on
+// `stream` (tallying into *tally) and then seal with flag_cache_filled(); kFlagsHit: *flags holds
+// valid flags (any cross-stream wait is already enqueued); kFlagsHitNothing: the mask is known
+// to have nothing to skip; kFlagsOff: no caching for this call.
+static int flag_cache_lookup(const FaMaskFwdArgs* a, const void* mask, long long bs, long long rs,
+                             int region_rows, size_t flag_bytes, cudaStream_t stream, int* slot_out,
+                             unsigned char** flags, int** tally) {
+    *slot_out = -1;
+    if (a->mask_version == 0 || flag_bytes > kFlagSlotBytes) return kFlagsOff;
+    cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+    if (cudaStreamIsCapturing(stream, &cap) != cudaSuccess) {
+        cudaGetLastError();
+        return kFlagsOff;
+    }
+    if (cap != cudaStreamCaptureStatusNone) return kFlagsOff;
+    std::lock_guard<std::mutex> lock(g_flag_mutex);
+    if (g_flag_tally == nullptr) {
+        void* ptr = nullptr;
+        if (cudaHostAlloc(&ptr, kFlagSlots * sizeof(int), cudaHostAllocMapped | cudaHostAllocPortable) != cudaSuccess) {
+            cudaGetLastError();
+            return kFlagsOff;
+        }
+        g_flag_tally = static_cast<int*>(ptr);
+        std::memset(g_flag_tally, 0, kFlagSlots * sizeof(int));
+    }
+    if (g_flag_cache_addr[a->device] == nullptr) {
+        void* ptr = nullptr;
+        if (cudaGetSymbolAddress(&ptr, g_flag_cache) != cudaSuccess || ptr == nullptr) {
+            cudaGetLastError();
+            return kFlagsOff;
+        }
+        g_flag_cache_addr[a->device] = ptr;
+    }
+    unsigned char* base = static_cast<unsigned char*>(g_flag_cache_addr[a->device]);
+    for (int i = 0; i < kFlagSlots; ++i) {
+        FlagEntry& e = g_flag_entries[i];
+        if (e.valid && e.mask == mask && e.bs == bs && e.rs == rs && e.B == a->batch && e.Sq == a->seqlen_q &&
+            e.Sk == a->seqlen_k && e.dtype == a->dtype && e.device == a->device &&
+            e.region_rows == region_rows && e.version == a->mask_version) {
+            // 0: the pre-pass has not reported yet; 1: nothing to skip; > 1: something
+            if (*static_cast<volatile int*>(g_flag_tally + i) == 1) return kFlagsHitNothing;
+            if (e.fill_stream != stream && cudaStreamWaitEvent(stream, e.filled, 0) != cudaSuccess) {
+                cudaGetLastError();
+                return kFlagsOff;
+            }
+            *slot_out = i;
+            *flags = base + static_cast<size_t>(i) * kFlagSlotBytes;
+            return kFlagsHit;
+        }
+    }
+    const int i = g_flag_next;
+    g_flag_next = (g_flag_next + 1) % kFlagSlots;
+    FlagEntry& e = g_flag_entries[i];
+    if (e.filled == nullptr &&
+        (cudaEventCreateWithFlags(&e.filled, cudaEventDisableTiming) != cudaSuccess ||
+         cudaEventCreateWithFlags(&e.last_read, cudaEventDisableTiming) != cudaSuccess)) {
+        cudaGetLastError();
+        e.filled = nullptr;
+        return kFlagsOff;
+    }
+    // whoever still reads the slot's old flags (possibly on another stream or device) goes first
+    if (e.valid && e.read_recorded && cudaStreamWaitEvent(stream, e.last_read, 0) != cudaSuccess) {
+        cudaGetLastError();
+        return kFlagsOff;
+    }
+    e.valid = false;                      // sealed by flag_cache_filled()
+    e.mask = mask; e.bs = bs; e.rs = rs; e.B = a->batch; e.Sq = a->seqlen_q; e.Sk = a->seqlen_k;
+    e.dtype = a->dtype; e.device = a->device; e.region_rows = region_rows; e.version = a->mask_version;
+    e.fill_stream = stream;
+    e.read_recorded = false;
+    g_flag_tally[i] = 0;
+    *slot_out = i;
+    *flags = base + static_cast<size_t>(i) * kFlagSlotBytes;
+    *tally = g_flag_tally + i;
+    return kFlagsFill;
+}
+
+static void flag_cache_filled(int slot, cudaStream_t stream) {
+    std::lock_guard<std::mutex> lock(g_flag_mutex);
+    FlagEntry& e = g_flag_entries[slot];
+    if (cudaEventRecord(e.filled, stream) == cudaSuccess) e.valid = true;
+    else cudaGetLastError();
+}
+
+static void flag_cache_read(int slot, cudaStream_t stream) {
+    std::lock_guard<std::mutex> lock(g_flag_mutex);
+    FlagEntry& e = g_flag_entries[slot];
+    if (cudaEventRecord(e.last_read, stream) == cudaSuccess) e.read_recorded = true;
+    else cudaGetLastError();
+}
+
 static int forward(const FaMaskFwdArgs* a, void* workspace, size_t workspace_bytes,
                    cudaStream_t stream, bool adaptive_skip = true) {
     FaMaskFwdPlan plan;
@@ -2243,15 +2366,31 @@ static int forward(const FaMaskFwdArgs* a, void* workspace, size_t workspace_byt
         mask_rs = pitch;
     }
     int* hint_counter = nullptr;
-    const bool run_classify = plan.tile_skip &&
-        want_classify(a, mask_ptr, mask_bs, mask_rs, adaptive_skip, stream, &hint_counter);
+    const int region_rows = plan.head_pairs ? kBlockM : 2 * kBlockM;
+    const int regions = ceil_div(a->seqlen_q, region_rows);
+    const size_t flag_bytes = static_cast<size_t>(a->batch) * regions * plan.kv_blocks;
+    // (the remembered flags describe the caller's own buffer: not for a re-pitched copy, whose
+    // address changes with the workspace, and not for the entry point that keeps no state)
+    int flag_slot = -1;
+    unsigned char* cached_flags = nullptr;
+    const int cache = (plan.tile_skip && adaptive_skip && !plan.mask_repitched)
+        ? flag_cache_lookup(a, mask_ptr, mask_bs, mask_rs, region_rows, flag_bytes, stream, &flag_slot,
+                            &cached_flags, &hint_counter)
+        : kFlagsOff;
+    const bool run_classify = plan.tile_skip && cache != kFlagsHit && cache != kFlagsHitNothing &&
+        (cache == kFlagsFill || want_classify(a, mask_ptr, mask_bs, mask_rs, adaptive_skip, stream, &hint_counter));
+    unsigned char* ws_flags = ws + (plan.mask_repitched
+        ? align256(static_cast<size_t>(a->batch) * a->seqlen_q * ((a->seqlen_k + 7) & ~7) * 2) : 0);
+    unsigned int* ws_unit_counter = reinterpret_cast<unsigned int*>(ws_flags + align256(flag_bytes));
+    if (cache == kFlagsHit) {
+        // no pre-pass: its other job, resetting the counter the units are handed out from, is done here
+        if (cudaMemsetAsync(ws_unit_counter, 0, sizeof(unsigned int), stream) != cudaSuccess) return cuda_failed(__LINE__);
+        kp.block_flags = cached_flags;
+        kp.unit_counter = ws_unit_counter;
+    }
     if (run_classify) {
-        unsigned char* flags = ws + (plan.mask_repitched
-            ? align256(static_cast<size_t>(a->batch) * a->seqlen_q * ((a->seqlen_k + 7) & ~7) * 2) : 0);
-        const int region_rows = plan.head_pairs ? kBlockM : 2 * kBlockM;
-        const int regions = ceil_div(a->seqlen_q, region_rows);
-        unsigned int* unit_counter = reinterpret_cast<unsigned int*>(
-            flags + align256(static_cast<size_t>(a->batch) * regions * plan.kv_blocks));
+        unsigned char* flags = cache == kFlagsFill ? cached_flags : ws_flags;
+        unsigned int* unit_counter = ws_unit_counter;
         const dim3 cgrid(plan.kv_blocks, regions, a->batch);
         const uint32_t ninf = a->dtype == FA_SM100_BF16 ? 0xFF80FF80u : 0xFC00FC00u;
         cudaLaunchConfig_t cfg = {};
@@ -2270,6 +2409,7 @@ static int forward(const FaMaskFwdArgs* a, void* workspace, size_t workspace_byt
         ++g_launches;
         kp.block_flags = flags;
         kp.unit_counter = unit_counter;
+        if (cache == kFlagsFill) flag_cache_filled(flag_slot, stream);
     }
     kp.out = a->out;
     kp.lse = a->lse;
@@ -2334,6 +2474,7 @@ static int forward(const FaMaskFwdArgs* a, void* workspace, size_t workspace_byt
                        : launch_fwd<64, false, false>(dev, slot, tq, tk, tv, tm, kp, grid, stream, chained);
     }
     if (rc != FA_SM100_OK) return rc;
+    if (flag_slot >= 0) flag_cache_read(flag_slot, stream);
     if (plan.num_splits > 1)
         rc = launch_combine(o_part, lse_part, a->out, a->lse,
                             plan.dual_split ? ceil_div(plan.num_splits, 2) : plan.num_splits, rows, d,

@@ -109,6 +109,15 @@ typedef struct FaMaskFwdArgs {
     int32_t num_splits;         /* 0 = choose, 1 = never split, n = force n KV splits */
     int32_t out_fp32;           /* 1: `out` is fp32 (normalised partial for a cross-GPU merge) */
     int32_t disable;            /* bit set of FA_SM100_NO_*: optimisations the caller switches off */
+    uint64_t mask_version;      /* 0: nothing is remembered about the mask's content.  Otherwise a number
+                                 * the caller changes whenever the content of this mask buffer changes:
+                                 * the result of the tile-skip pre-pass is then kept inside the library,
+                                 * per (mask pointer, strides, shape, dtype, device, version), and a
+                                 * later call with the same key skips the pre-pass (and, where the mask
+                                 * had nothing to skip, the skip list).  A caller that passes a stale
+                                 * version gets results for the old content.  Ignored while the stream
+                                 * is being captured, for a mask that has to be re-pitched (its copy
+                                 * lives in the workspace) and by fa_mask_fwd_sm100_static_scratch. */
 } FaMaskFwdArgs;
 
 /* What the launcher decided for a set of arguments; for tests and tuning. */

@@ -19,7 +19,7 @@ def from_bits(b: np.ndarray, dtype: str) -> torch.Tensor:
 
 
 def run_cabi(q, k, v, mask, *, num_splits=0, want_lse=False, out_fp32=False, device=0,
-             no_tile_skip=0, no_unit_cut=0, no_head_pairs=0):
+             no_tile_skip=0, no_unit_cut=0, no_head_pairs=0, mask_version=0):
     """q, k, v, mask: CUDA tensors.  Returns (out, lse or None, plan)."""
     B, H, Sq, d = q.shape
     Hk, Sk = k.shape[1], k.shape[2]
@@ -33,7 +33,7 @@ def run_cabi(q, k, v, mask, *, num_splits=0, want_lse=False, out_fp32=False, dev
         mask_seqlen_q=mask.shape[2], mask_seqlen_k=mask.shape[3],
         mask_batch_stride=mask.stride(0), mask_row_stride=mask.stride(2), device=device,
         num_splits=num_splits, out_fp32=1 if out_fp32 else 0, no_tile_skip=no_tile_skip, no_unit_cut=no_unit_cut,
-        no_head_pairs=no_head_pairs)
+        no_head_pairs=no_head_pairs, mask_version=mask_version)
     plan = _cabi.plan(args)
     nbytes = _cabi.workspace_bytes(args)
     ws = torch.empty(max(nbytes, 16), dtype=torch.uint8, device=q.device)

@@ -558,6 +558,45 @@ def test_tile_skipping_is_exact_on_structured_masks(dtype, case):
     check_against_oracle(out_skip, q, k, v, m, f"skip{case}")
 
 
+def test_block_flags_are_remembered_per_mask_version():
+    """With FaMaskFwdArgs.mask_version the pre-pass runs once per (mask buffer, version): later calls
+    launch the attention kernel alone and give the same bits; a new version re-reads the mask; a mask
+    with nothing to skip ends up on the plain kernel."""
+    b, h, hk, sq, sk, d = 2, 4, 2, 768, 1536, 128
+    q, k, v, _ = make_case(b, h, hk, sq, sk, d, torch.bfloat16, "zero", seed=37)
+    i = torch.arange(sq).view(sq, 1)
+    j = torch.arange(sk).view(1, sk)
+    def window(wd):
+        vis = (i + (sk - sq) - j >= 0) & (i + (sk - sq) - j < wd)
+        return torch.zeros(sq, sk).masked_fill(~vis, float("-inf")).to(torch.bfloat16).view(1, 1, sq, sk).expand(b, 1, sq, sk)
+    q, k, v = _cuda(q, k, v)
+    m = window(200).contiguous().cuda()
+    ref, _, plan = run_cabi(q, k, v, m, num_splits=1)
+    assert plan.tile_skip == 1
+    n0 = _cabi.launch_count()
+    first, _, _ = run_cabi(q, k, v, m, num_splits=1, mask_version=5)
+    n1 = _cabi.launch_count()
+    second, _, _ = run_cabi(q, k, v, m, num_splits=1, mask_version=5)
+    third, _, _ = run_cabi(q, k, v, m, num_splits=1, mask_version=5)
+    n3 = _cabi.launch_count()
+    assert n1 - n0 == 2 and n3 - n1 == 2                   # pre-pass + attention, then attention alone twice
+    assert torch.equal(first, ref) and torch.equal(second, ref) and torch.equal(third, ref)
+    m.copy_(window(500))                                    # new content in the same buffer: new version
+    new, _, _ = run_cabi(q, k, v, m, num_splits=1, mask_version=6)
+    assert _cabi.launch_count() - n3 == 2
+    check_against_oracle(new, q, k, v, m, "flags v6")
+    assert not torch.equal(new, ref)
+    # nothing to skip: after the pre-pass has reported, the calls run the kernel without a list
+    m2 = torch.zeros(b, 1, sq, sk, dtype=torch.bfloat16, device="cuda")
+    a1, _, _ = run_cabi(q, k, v, m2, num_splits=1, mask_version=1)
+    torch.cuda.synchronize()
+    n4 = _cabi.launch_count()
+    a2, _, _ = run_cabi(q, k, v, m2, num_splits=1, mask_version=1)
+    assert _cabi.launch_count() - n4 == 1
+    check_against_oracle(a2, q, k, v, m2, "flags nothing")
+    assert (a1.float() - a2.float()).abs().max().item() <= 4e-3        # (units may be cut in pieces now)
+
+
 def test_tile_skipping_everything_masked_and_trap_columns():
     """(a) a whole 256-row pair with no visible key at all: output 0, LSE -inf, no block is
     visited; (b) the only 'visible' entries of a region sit in columns >= Sk of a pre-padded

@@ -27,8 +27,8 @@ def test_library_exports_every_declared_symbol():
 
 
 def test_struct_sizes_match_header_layout():
-    # 2*4 + 6*8 + 8*4 + 2*8 + 4*4 = 120 ; 16*4 + 8 = 72
-    assert ctypes.sizeof(_cabi.FaMaskFwdArgs) == 120
+    # 2*4 + 6*8 + 8*4 + 2*8 + 4*4 + 8 = 128 ; 16*4 + 8 = 72
+    assert ctypes.sizeof(_cabi.FaMaskFwdArgs) == 128
     assert ctypes.sizeof(_cabi.FaMaskFwdPlan) == 72
     a = _cabi.make_args(batch=1, heads=1, heads_k=1, seqlen_q=8, seqlen_k=8, head_dim=64,
                         dtype=_cabi.BF16)
