@@ -10,6 +10,12 @@
 // the scratch with torch's caching allocator on q's device, then hands plain
 // pointers to the C ABI (include/fa_mask_fwd_sm100.h) on the current stream.
 //
+// A second operator, which the reference does not have, returns the log-sum-exp of every row
+// as well (natural log, fp32, (B, H, Sq); -inf for a fully masked row) - what a backward pass
+// or a merge of partial results over key ranges needs:
+//
+//   recsys_ops::mha_fwd_with_mask_lse(Tensor q, Tensor k, Tensor v, Tensor mask) -> (Tensor, Tensor)
+//
 // Differences from the reference, on purpose: K, V and the mask are never padded
 // here -- ragged seqlen_k is handled inside the launcher -- and CPU tensors raise
 // the same "only supported on CUDA" error the reference's CPU stub raises
@@ -23,8 +29,9 @@
 
 namespace {
 
-torch::Tensor mha_fwd_with_mask_cuda(const torch::Tensor& q, const torch::Tensor& k,
-                                     const torch::Tensor& v, const torch::Tensor& mask) {
+std::tuple<torch::Tensor, torch::Tensor> forward_cuda(const torch::Tensor& q, const torch::Tensor& k,
+                                                      const torch::Tensor& v, const torch::Tensor& mask,
+                                                      bool want_lse) {
     TORCH_CHECK(q.is_cuda(), "q must be a CUDA tensor");
     TORCH_CHECK(k.is_cuda(), "k must be a CUDA tensor");
     TORCH_CHECK(v.is_cuda(), "v must be a CUDA tensor");
@@ -62,6 +69,8 @@ torch::Tensor mha_fwd_with_mask_cuda(const torch::Tensor& q, const torch::Tensor
 
     const c10::cuda::CUDAGuard guard(q.device());
     auto out = torch::empty_like(q);
+    torch::Tensor lse;
+    if (want_lse) lse = torch::empty({B, H, Sq}, q.options().dtype(torch::kFloat32));
 
     FaMaskFwdArgs a{};
     a.struct_size = sizeof(FaMaskFwdArgs);
@@ -71,7 +80,7 @@ torch::Tensor mha_fwd_with_mask_cuda(const torch::Tensor& q, const torch::Tensor
     a.v = v.data_ptr();
     a.mask = mask.data_ptr();
     a.out = out.data_ptr();
-    a.lse = nullptr;
+    a.lse = want_lse ? lse.data_ptr<float>() : nullptr;
     a.batch = static_cast<int32_t>(B);
     a.heads = static_cast<int32_t>(H);
     a.heads_k = static_cast<int32_t>(Hk);
@@ -99,7 +108,12 @@ torch::Tensor mha_fwd_with_mask_cuda(const torch::Tensor& q, const torch::Tensor
     auto stream = at::cuda::getCurrentCUDAStream(q.get_device());
     rc = fa_mask_fwd_sm100(&a, ws_ptr, ws_bytes, static_cast<void*>(stream.stream()));
     TORCH_CHECK(rc == FA_SM100_OK, "mha_fwd_with_mask: ", fa_mask_fwd_sm100_strerror(rc));
-    return out;
+    return {out, lse};
+}
+
+torch::Tensor mha_fwd_with_mask_cuda(const torch::Tensor& q, const torch::Tensor& k,
+                                     const torch::Tensor& v, const torch::Tensor& mask) {
+    return std::get<0>(forward_cuda(q, k, v, mask, false));
 }
 
 torch::Tensor mha_fwd_with_mask_cpu(const torch::Tensor&, const torch::Tensor&,
@@ -114,14 +128,24 @@ torch::Tensor dispatch_mha_fwd_with_mask(const torch::Tensor& q, const torch::Te
                                 : mha_fwd_with_mask_cpu(q, k, v, mask);
 }
 
+std::tuple<torch::Tensor, torch::Tensor> dispatch_mha_fwd_with_mask_lse(const torch::Tensor& q,
+                                                                        const torch::Tensor& k,
+                                                                        const torch::Tensor& v,
+                                                                        const torch::Tensor& mask) {
+    TORCH_CHECK(q.device().is_cuda(), "mha_fwd_with_mask is only supported on CUDA");
+    return forward_cuda(q, k, v, mask, true);
+}
+
 }  // namespace
 
 TORCH_LIBRARY_FRAGMENT(recsys_ops, m) {
     m.def("mha_fwd_with_mask(Tensor q, Tensor k, Tensor v, Tensor mask) -> Tensor");
+    m.def("mha_fwd_with_mask_lse(Tensor q, Tensor k, Tensor v, Tensor mask) -> (Tensor, Tensor)");
 }
 
 TORCH_LIBRARY_IMPL(recsys_ops, CompositeExplicitAutograd, m) {
     m.impl("mha_fwd_with_mask", &dispatch_mha_fwd_with_mask);
+    m.impl("mha_fwd_with_mask_lse", &dispatch_mha_fwd_with_mask_lse);
 }
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {

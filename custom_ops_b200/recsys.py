@@ -301,9 +301,12 @@ class FAOps(CustomOps):
     required_ops = ["mha_fwd_with_mask"]
     op_schemas = {
         "mha_fwd_with_mask": "mha_fwd_with_mask(Tensor q, Tensor k, Tensor v, Tensor mask) -> Tensor",
+        "mha_fwd_with_mask_lse":
+            "mha_fwd_with_mask_lse(Tensor q, Tensor k, Tensor v, Tensor mask) -> (Tensor, Tensor)",
     }
-    fake_ops = ["mha_fwd_with_mask"]
-    optional_ops: list = []
+    fake_ops = ["mha_fwd_with_mask", "mha_fwd_with_mask_lse"]
+    # not in the reference: the same forward that also returns each row's log-sum-exp
+    optional_ops = ["mha_fwd_with_mask_lse"]
 
     def get_sources(self) -> list:
         return list(_build.TORCH_SOURCES) + list(_build.CABI_SOURCES)
@@ -323,6 +326,10 @@ class FAOps(CustomOps):
 
     def register_fake_impls(self) -> None:
         self.register_fake_for("mha_fwd_with_mask", lambda q, k, v, mask: torch.empty_like(q))
+        self.register_fake_for(
+            "mha_fwd_with_mask_lse",
+            lambda q, k, v, mask: (torch.empty_like(q),
+                                   q.new_empty((q.shape[0], q.shape[1], q.shape[2]), dtype=torch.float32)))
 
 
 class RecsysOps:
@@ -336,7 +343,7 @@ class RecsysOps:
     """
 
     _GROUP_CLASSES = {"fa": FAOps}
-    _OP_TO_GROUP = {"mha_fwd_with_mask": "fa"}
+    _OP_TO_GROUP = {"mha_fwd_with_mask": "fa", "mha_fwd_with_mask_lse": "fa"}
 
     def __init__(self, *, allow_jit: bool = True) -> None:
         self._allow_jit = bool(allow_jit)
@@ -471,3 +478,11 @@ class RecsysOps:
         ``(B, H, Sq, d)`` in q's dtype; a fully masked row is 0.
         """
         return self._dispatch(backend, "fa").mha_fwd_with_mask(q, k, v, mask)
+
+    def mha_fwd_with_mask_lse(self, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor,
+                              mask: torch.Tensor, backend: Optional[str] = None):
+        """``mha_fwd_with_mask`` that also returns the natural-log log-sum-exp of every row's
+        scaled, masked scores: ``(out, lse)`` with ``lse`` fp32 of shape ``(B, H, Sq)``, ``-inf``
+        for a fully masked row (the reference computes it, ``csrc/fa/common/softmax.h:145``, but
+        its operator does not return it)."""
+        return self._dispatch(backend, "fa").mha_fwd_with_mask_lse(q, k, v, mask)

@@ -292,6 +292,26 @@ def test_torch_operator_matches_cabi_and_errors():
         ops.mha_fwd_with_mask(qh.transpose(2, 3), qh, qh, torch.zeros(1, 1, 64, 64, device="cuda").half())
 
 
+def test_torch_operator_that_also_returns_the_lse():
+    """recsys_ops::mha_fwd_with_mask_lse: the same output bits plus the natural-log LSE per row,
+    -inf for a fully masked row; traceable through its fake implementation."""
+    from custom_ops_b200 import ops
+    q, k, v, m = make_case(2, 4, 2, 300, 515, 64, torch.float16, "all_masked_row", seed=41)
+    q, k, v, m = _cuda(q, k, v, m)
+    out = ops.mha_fwd_with_mask(q, k, v, m)
+    out2, lse = ops.mha_fwd_with_mask_lse(q, k, v, m)
+    assert torch.equal(out, out2) and lse.dtype == torch.float32 and tuple(lse.shape) == (2, 4, 300)
+    ref = oracle.lse_fp32(bits(q), bits(k), bits(m), "fp16")
+    got = lse.cpu().numpy()
+    assert np.isneginf(got[:, :, 0]).all() and np.isneginf(ref[:, :, 0]).all()
+    assert np.abs(got[:, :, 1:] - ref[:, :, 1:]).max() < 2e-3
+    fn = torch.compile(lambda a, b, c, d: torch.ops.recsys_ops.mha_fwd_with_mask_lse(a, b, c, d), fullgraph=True)
+    o3, l3 = fn(q, k, v, m)
+    assert torch.equal(o3, out) and torch.equal(l3, lse)
+    with pytest.raises(RuntimeError, match="only supported on CUDA"):
+        torch.ops.recsys_ops.mha_fwd_with_mask_lse(q.cpu(), k.cpu(), v.cpu(), m.cpu())
+
+
 def test_torch_compile_uses_fake_impl():
     from custom_ops_b200 import ops
     ops.ensure_loaded("fa")

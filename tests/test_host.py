@@ -161,7 +161,9 @@ def test_group_definition_matches_reference_contract():
     assert FAOps.namespace == "recsys_ops"
     assert FAOps.so_name == "recsys_fa_kernel"
     assert FAOps.required_ops == ["mha_fwd_with_mask"]
-    assert FAOps.fake_ops == ["mha_fwd_with_mask"]
+    # the reference's one operator is the required one; the LSE-returning variant is an extra
+    assert FAOps.optional_ops == ["mha_fwd_with_mask_lse"]
+    assert FAOps.fake_ops == ["mha_fwd_with_mask", "mha_fwd_with_mask_lse"]
     assert FAOps.op_schemas["mha_fwd_with_mask"] == \
         "mha_fwd_with_mask(Tensor q, Tensor k, Tensor v, Tensor mask) -> Tensor"
     assert FAOps.requires_cuda is True
