@@ -66,8 +66,8 @@ LEAD_IN_STEPS = 2      # untimed steps between the barrier and the first timed s
 
 # (constants from a capture, not measured live: they say which capture they come from)
 NCU_TRAFFIC_BYTES = {
-    "standard": 153.2e6,        # 135.06 MB read + 18.13 MB written (profiles/fa_mask_fwd_kernel_standard.md)
-    "splitkv_long": 281.6e6,    # 277.45 MB read + 4.11 MB written (profiles/fa_mask_fwd_kernel_splitkv_long.md)
+    "standard": 152.1e6,        # 134.69 MB read + 17.46 MB written (profiles/fa_mask_fwd_kernel_standard.md)
+    "splitkv_long": 281.6e6,    # 277.46 MB read + 4.11 MB written (profiles/fa_mask_fwd_kernel_splitkv_long.md)
 }
 
 
