@@ -171,7 +171,8 @@ __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
 enum : int { kPartWhole = 0, kPartTail = 1, kPartHead = 2 };
 
 // Unit board: what the scheduler warp publishes about one unit of work, a (split group,
-// 256-row query pair, head, batch) combination, as ints in shared memory.  A CTA runs two
+// 256-row query pair, head, batch) - or (split group, 128-row tile, pair of heads, batch) -
+// combination, as ints in shared memory.  A CTA runs two
 // softmax/MMA streams ("slots"); words kUiSlot + 4 * t + ... describe slot t.
 enum : int {
     kUiB = 0, kUiH = 1, kUiSgroup = 2, kUiKvPlane = 3, kUiQPlane = 4,
@@ -1433,7 +1434,7 @@ fa_mask_combine_kernel(const float* __restrict__ o_parts, const float* __restric
 }
 
 // ---------------------------------------------------------------------------------
-// Tile-skip pre-pass: one CTA per (key block, 256-row query pair, batch) decides whether the
+// Tile-skip pre-pass: one CTA per (key block, region of 256 or 128 query rows, batch) decides whether the
 // mask holds anything but -inf in that 256 x 128 region (only rows < Sq and columns < Sk
 // count).  flag = 1: the block must be visited; 0: every weight in it would be 0.
 // The mask rows are 16-byte aligned here (the launcher re-pitches otherwise).  A CTA stops
@@ -1789,7 +1790,8 @@ static int make_plan(const FaMaskFwdArgs* a, FaMaskFwdPlan* plan) {
     plan->blocks_per_split = bps;
     plan->q_tiles_per_cta = (a->seqlen_q > kBlockM || head_pairs) ? 2 : 1;
     plan->head_pairs = head_pairs ? 1 : 0;
-    // Units of (split, 256-row query pair, head, batch).  Pair mode is persistent: one CTA per
+    // Units of (split, 256-row query pair, head, batch), or (split, 128-row tile, pair of heads,
+    // batch) with head_pairs.  Pair mode is persistent: one CTA per
     // SM takes every grid_x-th unit, so the loads and the first MMA of a unit run under the
     // previous unit's epilogue.  Dual mode runs one unit per CTA.  (Splitting the units of a
     // half-empty last round into single-tile CTAs was measured and gains nothing: a CTA's time

@@ -133,7 +133,7 @@ typedef struct FaMaskFwdPlan {
     int32_t sm_count;
     int32_t dual_split;         /* 1: one query tile per CTA, two KV splits side by side */
     int32_t tile_skip;          /* 1: eligible for tile skipping: a pre-pass kernel finds the key blocks
-                                 * whose mask is -inf for a whole 256-row query pair and the attention
+                                 * whose mask is -inf for a whole 256-row query pair (128-row tile with head_pairs) and the attention
                                  * kernel does not visit them (exact: their weights are 0).  The
                                  * launcher drops the pre-pass for a while after it found nothing to
                                  * skip twice in a row for the same mask buffer and shape. */
