@@ -2198,9 +2198,9 @@ struct FlagEntry {
     cudaEvent_t filled = nullptr, last_read = nullptr;
     bool read_recorded = false;
 };
-static FlagEntry g_flag_entries[kFlagSlots];
-static int g_flag_next = 0;
-static int* g_flag_tally = nullptr;           // kFlagSlots ints, pinned + mapped
+static FlagEntry g_flag_entries[kMaxDevices][kFlagSlots];      // per device: its own slots and events
+static int g_flag_next[kMaxDevices] = {};
+static int* g_flag_tally = nullptr;           // kMaxDevices * kFlagSlots ints, pinned + mapped
 static void* g_flag_cache_addr[kMaxDevices] = {};
 static std::mutex g_flag_mutex;
 
@@ -2223,12 +2223,13 @@ static int flag_cache_lookup(const FaMaskFwdArgs* a, const void* mask, long long
     std::lock_guard<std::mutex> lock(g_flag_mutex);
     if (g_flag_tally == nullptr) {
         void* ptr = nullptr;
-        if (cudaHostAlloc(&ptr, kFlagSlots * sizeof(int), cudaHostAllocMapped | cudaHostAllocPortable) != cudaSuccess) {
+        if (cudaHostAlloc(&ptr, kMaxDevices * kFlagSlots * sizeof(int),
+                          cudaHostAllocMapped | cudaHostAllocPortable) != cudaSuccess) {
             cudaGetLastError();
             return kFlagsOff;
         }
         g_flag_tally = static_cast<int*>(ptr);
-        std::memset(g_flag_tally, 0, kFlagSlots * sizeof(int));
+        std::memset(g_flag_tally, 0, kMaxDevices * kFlagSlots * sizeof(int));
     }
     if (g_flag_cache_addr[a->device] == nullptr) {
         void* ptr = nullptr;
@@ -2239,13 +2240,15 @@ static int flag_cache_lookup(const FaMaskFwdArgs* a, const void* mask, long long
         g_flag_cache_addr[a->device] = ptr;
     }
     unsigned char* base = static_cast<unsigned char*>(g_flag_cache_addr[a->device]);
+    FlagEntry* entries = g_flag_entries[a->device];
+    int* tallies = g_flag_tally + a->device * kFlagSlots;
     for (int i = 0; i < kFlagSlots; ++i) {
-        FlagEntry& e = g_flag_entries[i];
+        FlagEntry& e = entries[i];
         if (e.valid && e.mask == mask && e.bs == bs && e.rs == rs && e.B == a->batch && e.Sq == a->seqlen_q &&
             e.Sk == a->seqlen_k && e.dtype == a->dtype && e.device == a->device &&
             e.region_rows == region_rows && e.version == a->mask_version) {
             // 0: the pre-pass has not reported yet; 1: nothing to skip; > 1: something
-            if (*static_cast<volatile int*>(g_flag_tally + i) == 1) return kFlagsHitNothing;
+            if (*static_cast<volatile int*>(tallies + i) == 1) return kFlagsHitNothing;
             if (e.fill_stream != stream && cudaStreamWaitEvent(stream, e.filled, 0) != cudaSuccess) {
                 cudaGetLastError();
                 return kFlagsOff;
@@ -2255,9 +2258,9 @@ static int flag_cache_lookup(const FaMaskFwdArgs* a, const void* mask, long long
             return kFlagsHit;
         }
     }
-    const int i = g_flag_next;
-    g_flag_next = (g_flag_next + 1) % kFlagSlots;
-    FlagEntry& e = g_flag_entries[i];
+    const int i = g_flag_next[a->device];
+    g_flag_next[a->device] = (i + 1) % kFlagSlots;
+    FlagEntry& e = entries[i];
     if (e.filled == nullptr &&
         (cudaEventCreateWithFlags(&e.filled, cudaEventDisableTiming) != cudaSuccess ||
          cudaEventCreateWithFlags(&e.last_read, cudaEventDisableTiming) != cudaSuccess)) {
@@ -2275,23 +2278,23 @@ static int flag_cache_lookup(const FaMaskFwdArgs* a, const void* mask, long long
     e.dtype = a->dtype; e.device = a->device; e.region_rows = region_rows; e.version = a->mask_version;
     e.fill_stream = stream;
     e.read_recorded = false;
-    g_flag_tally[i] = 0;
+    tallies[i] = 0;
     *slot_out = i;
     *flags = base + static_cast<size_t>(i) * kFlagSlotBytes;
-    *tally = g_flag_tally + i;
+    *tally = tallies + i;
     return kFlagsFill;
 }
 
-static void flag_cache_filled(int slot, cudaStream_t stream) {
+static void flag_cache_filled(int device, int slot, cudaStream_t stream) {
     std::lock_guard<std::mutex> lock(g_flag_mutex);
-    FlagEntry& e = g_flag_entries[slot];
+    FlagEntry& e = g_flag_entries[device][slot];
     if (cudaEventRecord(e.filled, stream) == cudaSuccess) e.valid = true;
     else cudaGetLastError();
 }
 
-static void flag_cache_read(int slot, cudaStream_t stream) {
+static void flag_cache_read(int device, int slot, cudaStream_t stream) {
     std::lock_guard<std::mutex> lock(g_flag_mutex);
-    FlagEntry& e = g_flag_entries[slot];
+    FlagEntry& e = g_flag_entries[device][slot];
     if (cudaEventRecord(e.last_read, stream) == cudaSuccess) e.read_recorded = true;
     else cudaGetLastError();
 }
@@ -2411,7 +2414,7 @@ static int forward(const FaMaskFwdArgs* a, void* workspace, size_t workspace_byt
         ++g_launches;
         kp.block_flags = flags;
         kp.unit_counter = unit_counter;
-        if (cache == kFlagsFill) flag_cache_filled(flag_slot, stream);
+        if (cache == kFlagsFill) flag_cache_filled(a->device, flag_slot, stream);
     }
     kp.out = a->out;
     kp.lse = a->lse;
@@ -2476,7 +2479,7 @@ static int forward(const FaMaskFwdArgs* a, void* workspace, size_t workspace_byt
                        : launch_fwd<64, false, false>(dev, slot, tq, tk, tv, tm, kp, grid, stream, chained);
     }
     if (rc != FA_SM100_OK) return rc;
-    if (flag_slot >= 0) flag_cache_read(flag_slot, stream);
+    if (flag_slot >= 0) flag_cache_read(a->device, flag_slot, stream);
     if (plan.num_splits > 1)
         rc = launch_combine(o_part, lse_part, a->out, a->lse,
                             plan.dual_split ? ceil_div(plan.num_splits, 2) : plan.num_splits, rows, d,
