@@ -617,6 +617,53 @@ def test_block_flags_are_remembered_per_mask_version():
     assert (a1.float() - a2.float()).abs().max().item() <= 4e-3        # (units may be cut in pieces now)
 
 
+def test_remembered_block_flags_across_streams_and_under_capture():
+    """Flags filled by a launch on one stream serve a launch on another (which waits for the
+    event of the fill); a captured launch remembers nothing, so its replays re-read the mask."""
+    b, h, hk, sq, sk, d = 1, 4, 4, 512, 2048, 64
+    q, k, v, _ = make_case(b, h, hk, sq, sk, d, torch.float16, "zero", seed=47)
+    i = torch.arange(sq).view(sq, 1)
+    j = torch.arange(sk).view(1, sk)
+    def band(lo, hi):
+        vis = (j >= i + lo) & (j < i + hi)
+        return torch.zeros(sq, sk).masked_fill(~vis, float("-inf")).to(torch.float16).view(1, 1, sq, sk).contiguous()
+    q, k, v = _cuda(q, k, v)
+    m = band(0, 300).cuda()
+    out = torch.empty_like(q)
+    args = _cabi.make_args(q=q.data_ptr(), k=k.data_ptr(), v=v.data_ptr(), mask=m.data_ptr(), out=out.data_ptr(),
+                           batch=b, heads=h, heads_k=hk, seqlen_q=sq, seqlen_k=sk, head_dim=d, dtype=_cabi.FP16,
+                           num_splits=1, mask_version=77)
+    assert _cabi.plan(args).tile_skip == 1
+    nbytes = _cabi.workspace_bytes(args)
+    ws = torch.empty(nbytes, dtype=torch.uint8, device="cuda")
+    ref, _, _ = run_cabi(q, k, v, m, num_splits=1)
+    s1, s2 = torch.cuda.Stream(), torch.cuda.Stream()
+    torch.cuda.synchronize()
+    n0 = _cabi.launch_count()
+    with torch.cuda.stream(s1):
+        _cabi.forward(args, ws.data_ptr(), nbytes, s1.cuda_stream)          # fills the slot
+    ws2 = torch.empty(nbytes, dtype=torch.uint8, device="cuda")
+    out2 = torch.empty_like(q)
+    args2 = _cabi.make_args(q=q.data_ptr(), k=k.data_ptr(), v=v.data_ptr(), mask=m.data_ptr(), out=out2.data_ptr(),
+                            batch=b, heads=h, heads_k=hk, seqlen_q=sq, seqlen_k=sk, head_dim=d, dtype=_cabi.FP16,
+                            num_splits=1, mask_version=77)
+    with torch.cuda.stream(s2):
+        _cabi.forward(args2, ws2.data_ptr(), nbytes, s2.cuda_stream)        # a hit, on another stream
+    torch.cuda.synchronize()
+    assert _cabi.launch_count() - n0 == 3
+    assert torch.equal(out, ref) and torch.equal(out2, ref)
+    # under capture nothing is remembered: the pre-pass is part of the graph and sees the new mask
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        _cabi.forward(args, ws.data_ptr(), nbytes, torch.cuda.current_stream().cuda_stream)
+    m.copy_(band(-100, 50))
+    graph.replay()
+    torch.cuda.synchronize()
+    check_against_oracle(out, q, k, v, m, "captured with a version")
+    assert not torch.equal(out, ref)
+    assert _cabi.device_status(0, clear=True) == 0
+
+
 def test_tile_skipping_everything_masked_and_trap_columns():
     """(a) a whole 256-row pair with no visible key at all: output 0, LSE -inf, no block is
     visited; (b) the only 'visible' entries of a region sit in columns >= Sk of a pre-padded
