@@ -29,6 +29,7 @@ EXPORTS = [
     "fa_mask_fwd_sm100",
     "fa_mask_fwd_sm100_static_scratch",
     "fa_mask_build_sm100",
+    "fa_mask_fwd_sm100_rule",
     "fa_mask_fwd_sm100_combine",
     "fa_mask_fwd_sm100_combine_packed",
     "fa_mask_fwd_sm100_combine_peers",
@@ -138,6 +139,9 @@ def load(path: str | None = None):
         ctypes.c_void_p, ctypes.c_int64, ctypes.c_int64, ctypes.c_int32, ctypes.c_int32, ctypes.c_uint32,
         ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int64, ctypes.c_int32, ctypes.c_int32, ctypes.c_int32,
         ctypes.c_int32, ctypes.c_void_p]
+    lib.fa_mask_fwd_sm100_rule.restype = ctypes.c_int
+    lib.fa_mask_fwd_sm100_rule.argtypes = [P(FaMaskFwdArgs), ctypes.c_int32, ctypes.c_int32, ctypes.c_void_p,
+                                           ctypes.c_void_p]
     lib.fa_mask_build_sm100.restype = ctypes.c_int
     lib.fa_mask_build_sm100.argtypes = [
         ctypes.c_void_p, ctypes.c_int32, ctypes.c_int32, ctypes.c_int32, ctypes.c_int32, ctypes.c_int32,
@@ -260,6 +264,13 @@ def device_status(device: int = 0, clear: bool = True) -> int:
     if rc not in (0, -10):
         check(rc)
     return int(st.value)
+
+
+def forward_rule(args: FaMaskFwdArgs, causal: int, window: int, valid_lens: int, stream: int):
+    """The forward for a mask given by rules (causal / sliding window / valid lengths) instead of
+    a tensor; ``valid_lens`` is a device pointer to ``batch`` int32 or 0."""
+    check(load().fa_mask_fwd_sm100_rule(ctypes.byref(args), int(causal), int(window), valid_lens or None,
+                                        stream or None))
 
 
 def launch_count() -> int:

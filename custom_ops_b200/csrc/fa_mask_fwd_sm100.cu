@@ -142,6 +142,12 @@ struct KParams {
     int mask_bcast;           // 1: one mask plane serves every batch element (batch stride 0)
     int test_stall_mask;      // test only: the mask producer loads nothing, so the waits for the
                               // mask run into their limit and the kernel reports it
+    // RULE kernels: no mask tensor.  Key j is visible to query row i when
+    //   lo < j <= hi,  hi = min(limit - 1, causal ? i + Sk - Sq : inf),  lo = window > 0 ? i + Sk - Sq - window : -1,
+    //   limit = min(Sk, valid_lens[batch]) (Sk without valid_lens)
+    // - the recipes of fa_mask_build_kernel, evaluated where they are used.
+    int rule_causal, rule_window;
+    const int* valid_lens;
 };
 
 template <bool BF16>
@@ -258,7 +264,7 @@ struct Ring {
     }
 };
 
-template <int D, bool BF16, bool LIST>
+template <int D, bool BF16, bool LIST, bool RULE = false>
 __global__ void __launch_bounds__(kThreads, 1)
 fa_mask_fwd_kernel(const __grid_constant__ CUtensorMap tm_q,
                    const __grid_constant__ CUtensorMap tm_k,
@@ -375,6 +381,18 @@ fa_mask_fwd_kernel(const __grid_constant__ CUtensorMap tm_q,
             }
             const int row0 = (dual || p.head_pairs) ? m0 : m0 + t * kBlockM;
             const bool on = dual ? (split < p.num_splits) : (row0 < p.Sq);
+            if constexpr (RULE) {
+                // the key blocks in which any row of the unit (both slots walk the same blocks)
+                // sees a key: between the first row's lower limit and the last row's upper one
+                const int rows = p.head_pairs ? kBlockM : 2 * kBlockM;
+                const int r_last = min(m0 + rows, p.Sq) - 1;
+                const int limit = p.valid_lens != nullptr ? min(p.Sk, p.valid_lens[b]) : p.Sk;
+                const int hi = p.rule_causal ? min(limit - 1, r_last + p.Sk - p.Sq) : limit - 1;
+                const int lo = p.rule_window > 0 ? m0 + p.Sk - p.Sq - p.rule_window : -1;
+                begin = max(lo + 1, 0) / kBlockN;
+                end = hi >= 0 ? hi / kBlockN + 1 : 0;
+                if (end < begin) end = begin;
+            }
             int n = on ? max(end - begin, 0) : -1;                 // -1: the slot does not exist
             if (LIST && on) n = count;                             // may be 0: nothing visible at all
             sts32(ui + 4 * (kUiSlot + 4 * t + kUiSplit), static_cast<uint32_t>(split));
@@ -562,7 +580,7 @@ fa_mask_fwd_kernel(const __grid_constant__ CUtensorMap tm_q,
                     const int begin_of[2] = {ui_get(ui, kUiSlot + kUiBegin), ui_get(ui, kUiSlot + 4 + kUiBegin)};
                     const int row0_of[2] = {ui_get(ui, kUiSlot + kUiRow0), ui_get(ui, kUiSlot + 4 + kUiRow0)};
                     const int b = p.mask_bcast ? 0 : ui_get(ui, kUiB);
-                    const int nmax = p.test_stall_mask ? 0 : max(n_of[0], n_of[1]);
+                    const int nmax = (RULE || p.test_stall_mask) ? 0 : max(n_of[0], n_of[1]);
                     for (int j = 0; ok && j < nmax; ++j) {
 #pragma unroll
                         for (int t = 0; t < 2; ++t) {
@@ -868,6 +886,17 @@ fa_mask_fwd_kernel(const __grid_constant__ CUtensorMap tm_q,
                 continue;
             }
             const int begin_t = ui_get(ui, kUiSlot + 4 * t + kUiBegin);
+            // RULE: the keys this thread's row sees, (rule_lo, rule_hi]
+            int rule_lo = -1, rule_hi = 0x3fffffff;
+            if constexpr (RULE) {
+                if (!warm) {
+                    const int bb = ui_get(ui, kUiB);
+                    const int limit = p.valid_lens != nullptr ? min(p.Sk, p.valid_lens[bb]) : p.Sk;
+                    const int diag = ui_get(ui, kUiSlot + 4 * t + kUiRow0) + row_in_tile + p.Sk - p.Sq;
+                    rule_hi = p.rule_causal ? min(limit - 1, diag) : limit - 1;
+                    rule_lo = p.rule_window > 0 ? diag - p.rule_window : -1;
+                }
+            }
 
             float m_ref = -INFINITY;     // reference maximum of the scaled, masked scores
             float l = 0.f;               // row sum relative to m_ref
@@ -885,13 +914,16 @@ fa_mask_fwd_kernel(const __grid_constant__ CUtensorMap tm_q,
                 // costs about 150 cycles even when the barrier has long completed, and here that
                 // latency falls into time the thread would spend waiting anyway, so that nothing
                 // but the wake-up from the score barrier stands between S and the first load.
-                bool ok = mbar_wait(dummy ? bar_scratch : bar_m_full + 8 * (2 * mt), par, abort_flag, p.status, kStSoftmaxMask);
-                ok = mbar_wait(dummy ? bar_scratch : bar_m_full + 8 * (2 * mt + 1), par, abort_flag, p.status, kStSoftmaxMask) && ok;
+                bool ok = true;
+                if constexpr (!RULE) {
+                    ok = mbar_wait(dummy ? bar_scratch : bar_m_full + 8 * (2 * mt), par, abort_flag, p.status, kStSoftmaxMask);
+                    ok = mbar_wait(dummy ? bar_scratch : bar_m_full + 8 * (2 * mt + 1), par, abort_flag, p.status, kStSoftmaxMask) && ok;
+                }
                 ok = mbar_wait(dummy ? bar_scratch : bar_s, par, abort_flag, p.status, kStSoftmaxS) && ok;
                 if (!__all_sync(0xffffffffu, ok)) { alive = false; break; }
                 tc_fence_after();
 
-                if (tail) {
+                if (tail && !RULE) {
                     // Last key block of a ragged Sk: columns >= Sk are masked whatever the mask
                     // tile holds there.  Their scores are overwritten with -inf in tensor memory
                     // before the row is loaded (s * scale + mask is then -inf for any finite mask
@@ -907,6 +939,56 @@ fa_mask_fwd_kernel(const __grid_constant__ CUtensorMap tm_q,
                 tmem_ld128(tS, sreg);
                 float2 x[kBlockN / 2];
                 float mt0 = -INFINITY, mt1 = -INFINITY;
+                if constexpr (RULE) {
+                    // No mask tile: the row sees the keys (rule_lo, rule_hi].  A block that every
+                    // row of the warp sees entirely needs nothing but the scale; otherwise the
+                    // row's 128 visibility bits are built from the two limits and each score gets
+                    // 0 or -inf added (columns beyond Sk lie beyond rule_hi).
+                    const int rel_lo = rule_lo - col0, rel_hi = rule_hi - col0;
+                    const bool plain = __all_sync(0xffffffffu, rel_lo < 0 && rel_hi >= kBlockN - 1) && !dummy;
+                    if (plain) {
+                        const float2 zero2 = make_float2(0.f, 0.f);
+#pragma unroll
+                        for (int i = 0; i < kBlockN; i += 4) {
+                            const float2 xa = __ffma2_rn(
+                                make_float2(__uint_as_float(sreg[i]), __uint_as_float(sreg[i + 1])), scale2, zero2);
+                            const float2 xb = __ffma2_rn(
+                                make_float2(__uint_as_float(sreg[i + 2]), __uint_as_float(sreg[i + 3])), scale2, zero2);
+                            x[i / 2] = xa;
+                            x[i / 2 + 1] = xb;
+                            mt0 = max3(mt0, xa.x, xb.x);
+                            mt1 = max3(mt1, xa.y, xb.y);
+                        }
+                    } else {
+                        uint32_t vis[4];
+#pragma unroll
+                        for (int w = 0; w < 4; ++w) {
+                            // bits [a, b) of word w: keys col0 + 32 w + [a, b) are visible
+                            const int a = min(max(rel_lo + 1 - 32 * w, 0), 32);
+                            const int b = min(max(rel_hi + 1 - 32 * w, 0), 32);
+                            const uint32_t below_b = b >= 32 ? 0xffffffffu : ((1u << b) - 1u);
+                            const uint32_t below_a = a >= 32 ? 0xffffffffu : ((1u << a) - 1u);
+                            vis[w] = b > a ? (below_b & ~below_a) : 0u;
+                        }
+#pragma unroll
+                        for (int i = 0; i < kBlockN; i += 4) {
+                            const uint32_t w = vis[i >> 5];
+                            const int sh = i & 31;
+                            const float2 a0 = make_float2(((w >> sh) & 1u) ? 0.f : -INFINITY,
+                                                          ((w >> (sh + 1)) & 1u) ? 0.f : -INFINITY);
+                            const float2 a1 = make_float2(((w >> (sh + 2)) & 1u) ? 0.f : -INFINITY,
+                                                          ((w >> (sh + 3)) & 1u) ? 0.f : -INFINITY);
+                            const float2 xa = __ffma2_rn(
+                                make_float2(__uint_as_float(sreg[i]), __uint_as_float(sreg[i + 1])), scale2, a0);
+                            const float2 xb = __ffma2_rn(
+                                make_float2(__uint_as_float(sreg[i + 2]), __uint_as_float(sreg[i + 3])), scale2, a1);
+                            x[i / 2] = xa;
+                            x[i / 2 + 1] = xb;
+                            mt0 = max3(mt0, xa.x, xb.x);
+                            mt1 = max3(mt1, xa.y, xb.y);
+                        }
+                    }
+                } else {
 #pragma unroll
                 for (int pn = 0; pn < 2; ++pn) {
 #pragma unroll
@@ -930,6 +1012,7 @@ fa_mask_fwd_kernel(const __grid_constant__ CUtensorMap tm_q,
                         }
                     }
                     mbar_arrive(dummy ? bar_scratch : bar_m_empty + 8 * (2 * mt + pn));      // panel may be refilled
+                }
                 }
                 const float mt = fmaxf(mt0, mt1);
 
@@ -1625,7 +1708,7 @@ struct DeviceInfo {
     unsigned int* status_ptr = nullptr;
     unsigned int* status_host = nullptr;     // pinned, mapped: the kernels' copy of a wait that gave up
     bool status_host_failed = false;
-    bool attr_set[8] = {false, false, false, false, false, false, false, false};
+    bool attr_set[12] = {false, false, false, false, false, false, false, false, false, false, false, false};
     bool queried = false;
 };
 static DeviceInfo g_dev[kMaxDevices];
@@ -1928,11 +2011,11 @@ static int get_maps(const MapKey& key, CUtensorMap* tq, CUtensorMap* tk, CUtenso
     return FA_SM100_OK;
 }
 
-template <int D, bool BF16, bool LIST>
+template <int D, bool BF16, bool LIST, bool RULE = false>
 static int launch_fwd(DeviceInfo* dev, int slot, const CUtensorMap& tq, const CUtensorMap& tk,
                       const CUtensorMap& tv, const CUtensorMap& tm, const KParams& kp, dim3 grid,
                       cudaStream_t stream, bool chained) {
-    auto kern = fa_mask_fwd_kernel<D, BF16, LIST>;
+    auto kern = fa_mask_fwd_kernel<D, BF16, LIST, RULE>;
     if (!dev->attr_set[slot]) {
         // The in-kernel register re-balancing is only sound for the register count it was
         // written for; refuse to launch a build that came out different.
@@ -2299,8 +2382,14 @@ static void flag_cache_read(int device, int slot, cudaStream_t stream) {
     else cudaGetLastError();
 }
 
+// A mask given by rules instead of a tensor (see KParams): what fa_mask_fwd_sm100_rule passes on.
+struct RuleSpec {
+    int causal, window;
+    const int* valid_lens;
+};
+
 static int forward(const FaMaskFwdArgs* a, void* workspace, size_t workspace_bytes,
-                   cudaStream_t stream, bool adaptive_skip = true) {
+                   cudaStream_t stream, bool adaptive_skip = true, const RuleSpec* rule = nullptr) {
     FaMaskFwdPlan plan;
     int rc = make_plan(a, &plan);
     if (rc != FA_SM100_OK) return rc;
@@ -2444,6 +2533,11 @@ static int forward(const FaMaskFwdArgs* a, void* workspace, size_t workspace_byt
     kp.scale = static_cast<float>(1.0 / std::sqrt(static_cast<double>(d)));
     kp.wait_kcycles = kMaxWaitKcycles;
     kp.mask_bcast = (mask_bs == 0 && a->batch > 1) ? 1 : 0;
+    if (rule != nullptr) {
+        kp.rule_causal = rule->causal;
+        kp.rule_window = rule->window;
+        kp.valid_lens = rule->valid_lens;
+    }
     if (a->disable & FA_SM100_TEST_STALL_MASK) {
         // test only: the mask never arrives, every wait gets a short limit (default 2 M cycles,
         // about a millisecond), the kernel gives up cleanly and reports it
@@ -2466,8 +2560,15 @@ static int forward(const FaMaskFwdArgs* a, void* workspace, size_t workspace_byt
     const bool chained = plan.mask_repitched || run_classify;
     const bool bf16 = a->dtype == FA_SM100_BF16;
     const bool list = kp.block_flags != nullptr;
-    const int slot = (d == 128 ? 0 : 2) + (bf16 ? 0 : 1) + (list ? 4 : 0);
-    if (d == 128) {
+    const int slot = (d == 128 ? 0 : 2) + (bf16 ? 0 : 1) + (list ? 4 : 0) + (rule != nullptr ? 8 : 0);
+    if (rule != nullptr) {
+        // (a rule launch is a single pass without a skip list: fa_mask_fwd_sm100_rule sees to that)
+        if (list || plan.num_splits != 1 || plan.unit_cut != 0 || plan.mask_repitched) return FA_SM100_ERR_SHAPE;
+        if (d == 128) rc = bf16 ? launch_fwd<128, true, false, true>(dev, slot, tq, tk, tv, tm, kp, grid, stream, chained)
+                                : launch_fwd<128, false, false, true>(dev, slot, tq, tk, tv, tm, kp, grid, stream, chained);
+        else rc = bf16 ? launch_fwd<64, true, false, true>(dev, slot, tq, tk, tv, tm, kp, grid, stream, chained)
+                       : launch_fwd<64, false, false, true>(dev, slot, tq, tk, tv, tm, kp, grid, stream, chained);
+    } else if (d == 128) {
         if (list) rc = bf16 ? launch_fwd<128, true, true>(dev, slot, tq, tk, tv, tm, kp, grid, stream, chained)
                             : launch_fwd<128, false, true>(dev, slot, tq, tk, tv, tm, kp, grid, stream, chained);
         else rc = bf16 ? launch_fwd<128, true, false>(dev, slot, tq, tk, tv, tm, kp, grid, stream, chained)
@@ -2673,6 +2774,27 @@ int fa_mask_build_sm100(void* mask, int32_t batch, int32_t seqlen_q, int32_t seq
     if (cudaPeekAtLastError() != cudaSuccess) return fa_sm100::cuda_failed(__LINE__);
     ++fa_sm100::g_launches;
     return FA_SM100_OK;
+}
+
+int fa_mask_fwd_sm100_rule(const FaMaskFwdArgs* args, int32_t causal, int32_t window, const int32_t* valid_lens,
+                           void* stream) {
+    if (args == nullptr) return FA_SM100_ERR_NULL;
+    if (args->struct_size != sizeof(FaMaskFwdArgs)) return FA_SM100_ERR_ABI;
+    if (window < 0) return FA_SM100_ERR_SHAPE;
+    // The same launch as for a mask tensor, as one pass over the keys with whole units and no
+    // pre-pass; the mask fields describe a one-plane placeholder that no kernel reads.
+    FaMaskFwdArgs a = *args;
+    a.mask = a.q;
+    a.mask_seqlen_q = a.seqlen_q;
+    a.mask_seqlen_k = a.seqlen_k;
+    a.mask_row_stride = (static_cast<int64_t>(a.seqlen_k) + 7) & ~static_cast<int64_t>(7);
+    a.mask_batch_stride = 0;
+    a.num_splits = 1;
+    a.out_fp32 = 0;
+    a.mask_version = 0;
+    a.disable |= FA_SM100_NO_TILE_SKIP | FA_SM100_NO_UNIT_CUT;
+    fa_sm100::RuleSpec rule{causal != 0 ? 1 : 0, window, valid_lens};
+    return fa_sm100::forward(&a, nullptr, 0, static_cast<cudaStream_t>(stream), true, &rule);
 }
 
 int fa_mask_fwd_sm100_static_scratch(const FaMaskFwdArgs* args, void* stream) {

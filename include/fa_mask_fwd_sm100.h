@@ -199,6 +199,17 @@ int fa_mask_fwd_sm100(const FaMaskFwdArgs* args, void* workspace, size_t workspa
  * unique to each launch (stale bytes never equal it) and taken back by their reader. */
 int fa_mask_fwd_sm100_static_scratch(const FaMaskFwdArgs* args, void* stream);
 
+/* The forward for a mask that is given by rules instead of a tensor - the recipes callers build
+ * their additive masks from (examples/custom_mask_demo.py:33-65) - so that no (B, 1, Sq, Sk) mask
+ * exists in memory at all:  key j is visible to query row i when  lo < j <= hi,
+ *   hi = min(limit - 1, causal ? i + Sk - Sq : +inf),   lo = window > 0 ? i + Sk - Sq - window : -1,
+ *   limit = min(Sk, valid_lens[batch])  (Sk when valid_lens is NULL; a device array of `batch` ints).
+ * Bit-identical to fa_mask_fwd_sm100 on the mask that fa_mask_build_sm100 writes for the same rules.
+ * The mask fields of `args` are ignored (mask may be NULL); `lse` is honoured; one pass over the
+ * keys whatever num_splits says; needs no workspace.  The reference has no such operator. */
+int fa_mask_fwd_sm100_rule(const FaMaskFwdArgs* args, int32_t causal, int32_t window, const int32_t* valid_lens,
+                           void* stream);
+
 /* Writes an additive mask (0 visible, -inf masked) of shape (batch, 1, seqlen_q, pitch) straight
  * into device memory from the rules callers of the operator otherwise spell out with a handful
  * of tensor operations (the reference's recipes, examples/custom_mask_demo.py:33-65; there is no

@@ -743,3 +743,42 @@ def test_rule_mask_equals_the_tensor_recipes(dtype, case):
     assert _cabi.plan(args).mask_repitched == 0
     assert torch.equal(ops.mha_fwd_with_mask(q, k, v, m), ops.mha_fwd_with_mask(q, k, v, ref.contiguous()))
 
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("case", [
+    (2, 4, 4, 512, 512, 128, dict(causal=True)),
+    (2, 8, 2, 1000, 1411, 64, dict(causal=True, window=300)),            # grouped heads run in pairs
+    (1, 4, 2, 700, 2053, 128, dict(window=129)),
+    (3, 2, 2, 300, 515, 128, dict(valid_lens=[515, 100, 0])),             # one batch element sees nothing
+    (2, 4, 1, 333, 900, 64, dict(causal=True, valid_lens=[640, 900])),
+    (1, 6, 3, 100, 3000, 128, dict(causal=True, window=1000)),            # one query tile, long keys
+    (1, 2, 2, 1100, 200, 128, dict(causal=True)),                         # more queries than keys: rows that see nothing
+    (2, 2, 2, 260, 260, 64, dict()),                                       # no rule at all: plain attention
+])
+def test_rule_attention_equals_the_operator_on_the_rule_mask(dtype, case):
+    """The rules evaluated inside the kernel (no mask in memory) give, bit for bit, what the operator
+    gives on the mask that rule_mask writes for the same rules; both match the oracle."""
+    from custom_ops_b200 import ops
+    from custom_ops_b200.masks import rule_attention, rule_mask
+    b, h, hk, sq, sk, d, rule = case
+    q, k, v, _ = make_case(b, h, hk, sq, sk, d, dtype, "zero", seed=53)
+    q, k, v = _cuda(q, k, v)
+    lens = torch.tensor(rule["valid_lens"], dtype=torch.int32) if "valid_lens" in rule else None
+    kw = dict(causal=rule.get("causal", False), window=rule.get("window", 0), valid_lens=lens)
+    m = rule_mask(b, sq, sk, dtype=dtype, **kw)
+    # (one pass over the keys and whole units, as the rule launch runs: splitting the keys or
+    # cutting a unit in pieces changes the rounding of the merge, nothing else)
+    want, want_lse, _ = run_cabi(q, k, v, m, num_splits=1, no_unit_cut=1, want_lse=True)
+    loose = ops.mha_fwd_with_mask(q, k, v, m)
+    n0 = _cabi.launch_count()
+    got, got_lse = rule_attention(q, k, v, return_lse=True, **kw)
+    torch.cuda.synchronize()
+    assert _cabi.launch_count() - n0 == 1
+    assert torch.equal(got, want)
+    assert (got.float() - loose.float()).abs().max().item() <= 4e-3
+    assert torch.equal(torch.isneginf(got_lse), torch.isneginf(want_lse))
+    fin = torch.isfinite(want_lse)
+    assert torch.equal(got_lse[fin], want_lse[fin])
+    check_against_oracle(got, q, k, v, m[..., :sk].contiguous(), f"rule{case}")
+    assert _cabi.device_status(0, clear=True) == 0
+
