@@ -141,7 +141,7 @@ def load(path: str | None = None):
         ctypes.c_int32, ctypes.c_void_p]
     lib.fa_mask_fwd_sm100_rule.restype = ctypes.c_int
     lib.fa_mask_fwd_sm100_rule.argtypes = [P(FaMaskFwdArgs), ctypes.c_int32, ctypes.c_int32, ctypes.c_void_p,
-                                           ctypes.c_void_p]
+                                           ctypes.c_void_p, ctypes.c_size_t, ctypes.c_void_p]
     lib.fa_mask_build_sm100.restype = ctypes.c_int
     lib.fa_mask_build_sm100.argtypes = [
         ctypes.c_void_p, ctypes.c_int32, ctypes.c_int32, ctypes.c_int32, ctypes.c_int32, ctypes.c_int32,
@@ -266,11 +266,16 @@ def device_status(device: int = 0, clear: bool = True) -> int:
     return int(st.value)
 
 
-def forward_rule(args: FaMaskFwdArgs, causal: int, window: int, valid_lens: int, stream: int):
+RULE_WORKSPACE_BYTES = 16
+
+
+def forward_rule(args: FaMaskFwdArgs, causal: int, window: int, valid_lens: int, stream: int,
+                 workspace: int = 0, workspace_nbytes: int = 0):
     """The forward for a mask given by rules (causal / sliding window / valid lengths) instead of
-    a tensor; ``valid_lens`` is a device pointer to ``batch`` int32 or 0."""
+    a tensor; ``valid_lens`` is a device pointer to ``batch`` int32 or 0; ``workspace``:
+    ``RULE_WORKSPACE_BYTES`` of device memory private to the call, or 0."""
     check(load().fa_mask_fwd_sm100_rule(ctypes.byref(args), int(causal), int(window), valid_lens or None,
-                                        stream or None))
+                                        workspace or None, workspace_nbytes, stream or None))
 
 
 def launch_count() -> int:

@@ -146,6 +146,8 @@ struct KParams {
     //   lo < j <= hi,  hi = min(limit - 1, causal ? i + Sk - Sq : inf),  lo = window > 0 ? i + Sk - Sq - window : -1,
     //   limit = min(Sk, valid_lens[batch]) (Sk without valid_lens)
     // - the recipes of fa_mask_build_kernel, evaluated where they are used.
+    // Units under a rule differ in length too: with `unit_counter` set the CTAs take them from it
+    // (the launcher zeroes it on the stream before the kernel).
     int rule_causal, rule_window;
     const int* valid_lens;
 };
@@ -659,7 +661,7 @@ fa_mask_fwd_kernel(const __grid_constant__ CUtensorMap tm_q,
                         peer_last = static_cast<int>(blockIdx.x) - (p.cut_units - 1);
                     }
                 } else if (k > 0) {
-                    if (LIST) {
+                    if (LIST || (RULE && p.unit_counter != nullptr)) {
                         if (lane == 0) unit = static_cast<int>(gridDim.x + atomicAdd(p.unit_counter, 1u));
                         unit = __shfl_sync(0xffffffffu, unit, 0);
                     } else {
@@ -2386,6 +2388,7 @@ static void flag_cache_read(int device, int slot, cudaStream_t stream) {
 struct RuleSpec {
     int causal, window;
     const int* valid_lens;
+    unsigned int* counter;            // a word of device memory private to the launch, or NULL
 };
 
 static int forward(const FaMaskFwdArgs* a, void* workspace, size_t workspace_bytes,
@@ -2537,6 +2540,12 @@ static int forward(const FaMaskFwdArgs* a, void* workspace, size_t workspace_byt
         kp.rule_causal = rule->causal;
         kp.rule_window = rule->window;
         kp.valid_lens = rule->valid_lens;
+        if (rule->counter != nullptr) {
+            // (a compare-and-swap counter that tolerates any content was measured first: with 148
+            // CTAs drawing in waves its retries are quadratic and cost 100 us per launch)
+            if (cudaMemsetAsync(rule->counter, 0, sizeof(unsigned int), stream) != cudaSuccess) return cuda_failed(__LINE__);
+            kp.unit_counter = rule->counter;
+        }
     }
     if (a->disable & FA_SM100_TEST_STALL_MASK) {
         // test only: the mask never arrives, every wait gets a short limit (default 2 M cycles,
@@ -2777,10 +2786,13 @@ int fa_mask_build_sm100(void* mask, int32_t batch, int32_t seqlen_q, int32_t seq
 }
 
 int fa_mask_fwd_sm100_rule(const FaMaskFwdArgs* args, int32_t causal, int32_t window, const int32_t* valid_lens,
-                           void* stream) {
+                           void* workspace, size_t workspace_bytes, void* stream) {
     if (args == nullptr) return FA_SM100_ERR_NULL;
     if (args->struct_size != sizeof(FaMaskFwdArgs)) return FA_SM100_ERR_ABI;
     if (window < 0) return FA_SM100_ERR_SHAPE;
+    if (workspace != nullptr && (workspace_bytes < FA_SM100_RULE_WORKSPACE_BYTES ||
+                                 (reinterpret_cast<uintptr_t>(workspace) & 15u) != 0))
+        return FA_SM100_ERR_WORKSPACE;
     // The same launch as for a mask tensor, as one pass over the keys with whole units and no
     // pre-pass; the mask fields describe a one-plane placeholder that no kernel reads.
     FaMaskFwdArgs a = *args;
@@ -2793,7 +2805,7 @@ int fa_mask_fwd_sm100_rule(const FaMaskFwdArgs* args, int32_t causal, int32_t wi
     a.out_fp32 = 0;
     a.mask_version = 0;
     a.disable |= FA_SM100_NO_TILE_SKIP | FA_SM100_NO_UNIT_CUT;
-    fa_sm100::RuleSpec rule{causal != 0 ? 1 : 0, window, valid_lens};
+    fa_sm100::RuleSpec rule{causal != 0 ? 1 : 0, window, valid_lens, static_cast<unsigned int*>(workspace)};
     return fa_sm100::forward(&a, nullptr, 0, static_cast<cudaStream_t>(stream), true, &rule);
 }
 

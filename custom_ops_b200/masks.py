@@ -93,7 +93,10 @@ def rule_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, causal:
                            seqlen_k=Sk, head_dim=d, dtype=_cabi.BF16 if q.dtype == torch.bfloat16 else _cabi.FP16,
                            device=q.device.index)
     stream = torch.cuda.current_stream(q.device)
-    _cabi.forward_rule(args, int(bool(causal)), int(window), lens_ptr, stream.cuda_stream)
+    # the counter the CTAs take their units from (any content; private to this call)
+    ws = torch.empty(_cabi.RULE_WORKSPACE_BYTES, dtype=torch.uint8, device=q.device)
+    _cabi.forward_rule(args, int(bool(causal)), int(window), lens_ptr, stream.cuda_stream, ws.data_ptr(),
+                       _cabi.RULE_WORKSPACE_BYTES)
     if valid_lens is not None:
         valid_lens.record_stream(stream)
     return (out, lse) if return_lse else out

@@ -206,9 +206,15 @@ int fa_mask_fwd_sm100_static_scratch(const FaMaskFwdArgs* args, void* stream);
  *   limit = min(Sk, valid_lens[batch])  (Sk when valid_lens is NULL; a device array of `batch` ints).
  * Bit-identical to fa_mask_fwd_sm100 on the mask that fa_mask_build_sm100 writes for the same rules.
  * The mask fields of `args` are ignored (mask may be NULL); `lse` is honoured; one pass over the
- * keys whatever num_splits says; needs no workspace.  The reference has no such operator. */
+ * keys whatever num_splits says.  `workspace`: FA_SM100_RULE_WORKSPACE_BYTES of device memory, 16-byte
+ * aligned, that no other call uses until this one has finished - the counter the CTAs take their
+ * units from (units differ in length under a rule; the call zeroes it on the stream with a
+ * cudaMemsetAsync ahead of the kernel); NULL: every CTA takes a fixed
+ * share of the units instead (slower where the lengths differ much).  The reference has no such
+ * operator. */
+#define FA_SM100_RULE_WORKSPACE_BYTES 16
 int fa_mask_fwd_sm100_rule(const FaMaskFwdArgs* args, int32_t causal, int32_t window, const int32_t* valid_lens,
-                           void* stream);
+                           void* workspace, size_t workspace_bytes, void* stream);
 
 /* Writes an additive mask (0 visible, -inf masked) of shape (batch, 1, seqlen_q, pitch) straight
  * into device memory from the rules callers of the operator otherwise spell out with a handful

@@ -780,5 +780,29 @@ def test_rule_attention_equals_the_operator_on_the_rule_mask(dtype, case):
     fin = torch.isfinite(want_lse)
     assert torch.equal(got_lse[fin], want_lse[fin])
     check_against_oracle(got, q, k, v, m[..., :sk].contiguous(), f"rule{case}")
+    # without the counter every CTA takes a fixed share of the units: same bits; and the counter
+    # word may hold anything, also what the previous launch or a replayed graph left there
+    out2 = torch.empty_like(q)
+    args = _cabi.make_args(q=q.data_ptr(), k=k.data_ptr(), v=v.data_ptr(), mask=0, out=out2.data_ptr(), batch=b,
+                           heads=h, heads_k=hk, seqlen_q=sq, seqlen_k=sk, head_dim=d,
+                           dtype=_cabi.BF16 if dtype == torch.bfloat16 else _cabi.FP16)
+    lens_dev = lens.cuda() if lens is not None else None
+    lp = lens_dev.data_ptr() if lens_dev is not None else 0
+    stream = torch.cuda.current_stream().cuda_stream
+    _cabi.forward_rule(args, int(kw["causal"]), kw["window"], lp, stream)
+    torch.cuda.synchronize()
+    assert torch.equal(out2, want)
+    ws = torch.full((_cabi.RULE_WORKSPACE_BYTES,), 0xA5, dtype=torch.uint8, device="cuda")
+    _cabi.forward_rule(args, int(kw["causal"]), kw["window"], lp, stream, ws.data_ptr(), _cabi.RULE_WORKSPACE_BYTES)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        _cabi.forward_rule(args, int(kw["causal"]), kw["window"], lp, torch.cuda.current_stream().cuda_stream,
+                           ws.data_ptr(), _cabi.RULE_WORKSPACE_BYTES)
+    for _ in range(3):
+        out2.zero_()
+        graph.replay()
+        torch.cuda.synchronize()
+        assert torch.equal(out2, want)
     assert _cabi.device_status(0, clear=True) == 0
 
