@@ -16,6 +16,12 @@
 //
 //   recsys_ops::mha_fwd_with_mask_lse(Tensor q, Tensor k, Tensor v, Tensor mask) -> (Tensor, Tensor)
 //
+// A third one takes the mask as a rule instead of a tensor (causal, sliding window, valid
+// lengths: the recipes of examples/custom_mask_demo.py:33-65) and evaluates it inside the kernel:
+//
+//   recsys_ops::mha_fwd_rule_mask(Tensor q, Tensor k, Tensor v, bool causal, int window,
+//                                 Tensor? valid_lens) -> Tensor
+//
 // Differences from the reference, on purpose: K, V and the mask are never padded
 // here -- ragged seqlen_k is handled inside the launcher -- and CPU tensors raise
 // the same "only supported on CUDA" error the reference's CPU stub raises
@@ -128,6 +134,51 @@ torch::Tensor dispatch_mha_fwd_with_mask(const torch::Tensor& q, const torch::Te
                                 : mha_fwd_with_mask_cpu(q, k, v, mask);
 }
 
+torch::Tensor mha_fwd_rule_mask(const torch::Tensor& q, const torch::Tensor& k, const torch::Tensor& v,
+                                bool causal, int64_t window, const c10::optional<torch::Tensor>& valid_lens) {
+    TORCH_CHECK(q.is_cuda() && k.is_cuda() && v.is_cuda(), "mha_fwd_rule_mask is only supported on CUDA");
+    const bool is_bf16 = q.dtype() == torch::kBFloat16;
+    TORCH_CHECK(is_bf16 || q.dtype() == torch::kHalf, "q must be float16 or bfloat16");
+    TORCH_CHECK(k.dtype() == q.dtype() && v.dtype() == q.dtype(), "k and v dtype must match q");
+    TORCH_CHECK(q.is_contiguous() && k.is_contiguous() && v.is_contiguous(), "q, k, v must be contiguous");
+    TORCH_CHECK(q.dim() == 4 && k.dim() == 4 && v.dim() == 4, "q must be (B, H, Sq, d), k and v (B, Hk, Sk, d)");
+    const int64_t B = q.size(0), H = q.size(1), Sq = q.size(2), d = q.size(3);
+    const int64_t Hk = k.size(1), Sk = k.size(2);
+    TORCH_CHECK(k.size(0) == B && v.sizes() == k.sizes() && k.size(3) == d, "shape mismatch between q, k and v");
+    TORCH_CHECK(Hk > 0 && H % Hk == 0, "n_heads must be divisible by n_kv_heads (GQA)");
+    TORCH_CHECK(d == 64 || d == 128, "Only head_dim=64 or head_dim=128 is supported");
+    TORCH_CHECK(window >= 0, "window must be >= 0");
+    TORCH_CHECK(k.device() == q.device() && v.device() == q.device(), "q, k, v must be on the same device");
+    const c10::cuda::CUDAGuard guard(q.device());
+    torch::Tensor lens;
+    if (valid_lens.has_value() && valid_lens->defined()) {
+        TORCH_CHECK(valid_lens->numel() == B, "valid_lens must hold one length per batch element");
+        lens = valid_lens->to(q.device(), torch::kInt32).contiguous();
+    }
+    auto out = torch::empty_like(q);
+    auto ws = torch::empty({FA_SM100_RULE_WORKSPACE_BYTES}, torch::TensorOptions().dtype(torch::kUInt8).device(q.device()));
+    FaMaskFwdArgs a{};
+    a.struct_size = sizeof(FaMaskFwdArgs);
+    a.device = q.get_device();
+    a.q = q.data_ptr();
+    a.k = k.data_ptr();
+    a.v = v.data_ptr();
+    a.out = out.data_ptr();
+    a.batch = static_cast<int32_t>(B);
+    a.heads = static_cast<int32_t>(H);
+    a.heads_k = static_cast<int32_t>(Hk);
+    a.seqlen_q = static_cast<int32_t>(Sq);
+    a.seqlen_k = static_cast<int32_t>(Sk);
+    a.head_dim = static_cast<int32_t>(d);
+    a.dtype = is_bf16 ? FA_SM100_BF16 : FA_SM100_FP16;
+    auto stream = at::cuda::getCurrentCUDAStream(q.get_device());
+    const int rc = fa_mask_fwd_sm100_rule(&a, causal ? 1 : 0, static_cast<int32_t>(window),
+                                          lens.defined() ? lens.data_ptr<int32_t>() : nullptr, ws.data_ptr(),
+                                          FA_SM100_RULE_WORKSPACE_BYTES, static_cast<void*>(stream.stream()));
+    TORCH_CHECK(rc == FA_SM100_OK, "mha_fwd_rule_mask: ", fa_mask_fwd_sm100_strerror(rc));
+    return out;
+}
+
 std::tuple<torch::Tensor, torch::Tensor> dispatch_mha_fwd_with_mask_lse(const torch::Tensor& q,
                                                                         const torch::Tensor& k,
                                                                         const torch::Tensor& v,
@@ -141,11 +192,13 @@ std::tuple<torch::Tensor, torch::Tensor> dispatch_mha_fwd_with_mask_lse(const to
 TORCH_LIBRARY_FRAGMENT(recsys_ops, m) {
     m.def("mha_fwd_with_mask(Tensor q, Tensor k, Tensor v, Tensor mask) -> Tensor");
     m.def("mha_fwd_with_mask_lse(Tensor q, Tensor k, Tensor v, Tensor mask) -> (Tensor, Tensor)");
+    m.def("mha_fwd_rule_mask(Tensor q, Tensor k, Tensor v, bool causal, int window, Tensor? valid_lens) -> Tensor");
 }
 
 TORCH_LIBRARY_IMPL(recsys_ops, CompositeExplicitAutograd, m) {
     m.impl("mha_fwd_with_mask", &dispatch_mha_fwd_with_mask);
     m.impl("mha_fwd_with_mask_lse", &dispatch_mha_fwd_with_mask_lse);
+    m.impl("mha_fwd_rule_mask", &mha_fwd_rule_mask);
 }
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {

@@ -303,10 +303,13 @@ class FAOps(CustomOps):
         "mha_fwd_with_mask": "mha_fwd_with_mask(Tensor q, Tensor k, Tensor v, Tensor mask) -> Tensor",
         "mha_fwd_with_mask_lse":
             "mha_fwd_with_mask_lse(Tensor q, Tensor k, Tensor v, Tensor mask) -> (Tensor, Tensor)",
+        "mha_fwd_rule_mask":
+            "mha_fwd_rule_mask(Tensor q, Tensor k, Tensor v, bool causal, int window, Tensor? valid_lens) -> Tensor",
     }
-    fake_ops = ["mha_fwd_with_mask", "mha_fwd_with_mask_lse"]
-    # not in the reference: the same forward that also returns each row's log-sum-exp
-    optional_ops = ["mha_fwd_with_mask_lse"]
+    fake_ops = ["mha_fwd_with_mask", "mha_fwd_with_mask_lse", "mha_fwd_rule_mask"]
+    # not in the reference: the same forward that also returns each row's log-sum-exp, and the
+    # forward for a mask given as a rule (causal / sliding window / valid lengths)
+    optional_ops = ["mha_fwd_with_mask_lse", "mha_fwd_rule_mask"]
 
     def get_sources(self) -> list:
         return list(_build.TORCH_SOURCES) + list(_build.CABI_SOURCES)
@@ -330,6 +333,8 @@ class FAOps(CustomOps):
             "mha_fwd_with_mask_lse",
             lambda q, k, v, mask: (torch.empty_like(q),
                                    q.new_empty((q.shape[0], q.shape[1], q.shape[2]), dtype=torch.float32)))
+        self.register_fake_for("mha_fwd_rule_mask",
+                               lambda q, k, v, causal, window, valid_lens: torch.empty_like(q))
 
 
 class RecsysOps:
@@ -343,7 +348,7 @@ class RecsysOps:
     """
 
     _GROUP_CLASSES = {"fa": FAOps}
-    _OP_TO_GROUP = {"mha_fwd_with_mask": "fa", "mha_fwd_with_mask_lse": "fa"}
+    _OP_TO_GROUP = {"mha_fwd_with_mask": "fa", "mha_fwd_with_mask_lse": "fa", "mha_fwd_rule_mask": "fa"}
 
     def __init__(self, *, allow_jit: bool = True) -> None:
         self._allow_jit = bool(allow_jit)
@@ -486,3 +491,13 @@ class RecsysOps:
         for a fully masked row (the reference computes it, ``csrc/fa/common/softmax.h:145``, but
         its operator does not return it)."""
         return self._dispatch(backend, "fa").mha_fwd_with_mask_lse(q, k, v, mask)
+
+    def mha_fwd_rule_mask(self, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, causal: bool = False,
+                          window: int = 0, valid_lens: Optional[torch.Tensor] = None,
+                          backend: Optional[str] = None) -> torch.Tensor:
+        """The forward for a mask given as a rule instead of a tensor: key ``j`` is visible to query
+        ``i`` when ``j < valid_lens[b]`` (if given), ``j <= i + Sk - Sq`` (if ``causal``) and
+        ``j > i + Sk - Sq - window`` (if ``window > 0``) - the recipes callers build their additive
+        masks from (``examples/custom_mask_demo.py:33-65``), evaluated inside the kernel.
+        Bit-identical to ``mha_fwd_with_mask`` on ``masks.rule_mask`` of the same rule."""
+        return self._dispatch(backend, "fa").mha_fwd_rule_mask(q, k, v, bool(causal), int(window), valid_lens)

@@ -57,7 +57,7 @@ def test_export_describes_both_libraries(exported):
     assert meta["producer"] == "custom_ops_b200" and meta["format_version"] == deploy.FORMAT_VERSION
     assert meta["namespace"] == "recsys_ops" and meta["so_name"] == "recsys_fa_kernel"
     assert meta["required_ops"] == ["mha_fwd_with_mask"]
-    assert meta["fake_ops"] == ["mha_fwd_with_mask", "mha_fwd_with_mask_lse"]
+    assert meta["fake_ops"] == ["mha_fwd_rule_mask", "mha_fwd_with_mask", "mha_fwd_with_mask_lse"]
     assert meta["schemas"]["mha_fwd_with_mask"].startswith("recsys_ops::mha_fwd_with_mask(Tensor q")
     assert meta["with_cuda"] is True and meta["cuda_arch_list"] == ["10.0a"]
     assert meta["library"]["filename"] == os.path.basename(exported)

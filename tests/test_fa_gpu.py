@@ -776,6 +776,12 @@ def test_rule_attention_equals_the_operator_on_the_rule_mask(dtype, case):
     assert _cabi.launch_count() - n0 == 1
     assert torch.equal(got, want)
     assert (got.float() - loose.float()).abs().max().item() <= 4e-3
+    # the torch operator, eager and through torch.compile (fake implementation registered)
+    assert torch.equal(ops.mha_fwd_rule_mask(q, k, v, kw["causal"], kw["window"], lens), want)
+    if case[0] == 2 and "window" in rule:
+        fn = torch.compile(lambda a_, b_, c_: torch.ops.recsys_ops.mha_fwd_rule_mask(a_, b_, c_, True, 300, None),
+                           fullgraph=True)
+        assert torch.equal(fn(q, k, v), want)
     assert torch.equal(torch.isneginf(got_lse), torch.isneginf(want_lse))
     fin = torch.isfinite(want_lse)
     assert torch.equal(got_lse[fin], want_lse[fin])

@@ -162,8 +162,8 @@ def test_group_definition_matches_reference_contract():
     assert FAOps.so_name == "recsys_fa_kernel"
     assert FAOps.required_ops == ["mha_fwd_with_mask"]
     # the reference's one operator is the required one; the LSE-returning variant is an extra
-    assert FAOps.optional_ops == ["mha_fwd_with_mask_lse"]
-    assert FAOps.fake_ops == ["mha_fwd_with_mask", "mha_fwd_with_mask_lse"]
+    assert FAOps.optional_ops == ["mha_fwd_with_mask_lse", "mha_fwd_rule_mask"]
+    assert FAOps.fake_ops == ["mha_fwd_with_mask", "mha_fwd_with_mask_lse", "mha_fwd_rule_mask"]
     assert FAOps.op_schemas["mha_fwd_with_mask"] == \
         "mha_fwd_with_mask(Tensor q, Tensor k, Tensor v, Tensor mask) -> Tensor"
     assert FAOps.requires_cuda is True
