@@ -706,9 +706,17 @@ def run_ours(args, w):
     launches_per_step = (1 + (1 if plan.num_splits > 1 else 0) + (1 if plan.mask_repitched else 0)
                          + (1 if plan.tile_skip else 0))
 
+    # --mask-as-rule (gqa_window only, whose mask is "causal, window of 512 keys"): the kernel-only
+    # steps run the rule forward, which reads no mask at all; for profiling that kernel.
+    as_rule = bool(getattr(args, "mask_as_rule", False)) and w.mask_kind == "causal_window" and not cross_split
+    rule_ws = torch.empty(_cabi.RULE_WORKSPACE_BYTES, dtype=torch.uint8, device=dev)
+
     def step_kernel():
         if cross_split:
             return parallel.splitkv_forward(q, k, v, m)
+        if as_rule:
+            _cabi.forward_rule(cargs, 1, 512, 0, stream.cuda_stream, rule_ws.data_ptr(), _cabi.RULE_WORKSPACE_BYTES)
+            return
         _cabi.forward(cargs_sets[step_no[0] % n_sets], ws.data_ptr(), ws_bytes, stream.cuda_stream)
         step_no[0] += 1
 
@@ -842,7 +850,7 @@ def run_ours(args, w):
             "higher_is_better": True, "scaling": "strong" if (cross_split or strong) else "weak",
             "vs_baseline": None,
             "dtype": "bf16" if w.dtype == torch.bfloat16 else "fp16", "data": "synthetic",
-            "config": {"workload": w.name, "shape": shape_str(w),
+            "config": {"workload": w.name, "shape": shape_str(w), "mask_as_rule": as_rule,
                        "parallelism": (f"keys split across {world} ranks, NCCL all-gather of fp32 "
                                        f"partials + LSE merge" if cross_split else
                                        f"(batch, kv-head) units of one problem spread over {world} rank(s), no collective"
@@ -901,6 +909,9 @@ def main():
                     help="with --gpus N > 1: weak = every rank its own batch shard (default); strong = one "
                          "problem's (batch, kv-head) units spread over the ranks")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--mask-as-rule", action="store_true",
+                    help="--workload gqa_window only: the kernel-only steps give the mask as a rule "
+                         "(fa_mask_fwd_sm100_rule) instead of a tensor")
     ap.add_argument("--only-headline", action="store_true",
                     help="skip the all_configs / strong_scaling / cross_gpu_splitkv sub-records")
     args = ap.parse_args()
