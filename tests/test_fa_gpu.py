@@ -754,6 +754,9 @@ def test_rule_mask_equals_the_tensor_recipes(dtype, case):
     (1, 6, 3, 100, 3000, 128, dict(causal=True, window=1000)),            # one query tile, long keys
     (1, 2, 2, 1100, 200, 128, dict(causal=True)),                         # more queries than keys: rows that see nothing
     (2, 2, 2, 260, 260, 64, dict()),                                       # no rule at all: plain attention
+    (2, 4, 4, 1, 777, 128, dict(causal=True, valid_lens=[5000, 3])),      # one query row; a length beyond Sk
+    (1, 2, 1, 130, 131, 64, dict(causal=True, window=100000)),            # a window wider than everything
+    (1, 4, 2, 513, 1, 128, dict(causal=True)),                            # a single key
 ])
 def test_rule_attention_equals_the_operator_on_the_rule_mask(dtype, case):
     """The rules evaluated inside the kernel (no mask in memory) give, bit for bit, what the operator
